@@ -124,7 +124,8 @@ class CacheManager:
             if device is not None:
                 shape = (self.num_pages, need.kv_heads, self.page_size, need.head_dim)
                 st.k_pages = torch.empty(shape, dtype=dtype, device=device)
-                st.v_pages = torch.empty(shape[:3] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
+                if not need.values_in_keys:
+                    st.v_pages = torch.empty(shape[:3] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
             return st
         if isinstance(need, StateNeed):
             self.has_state = True

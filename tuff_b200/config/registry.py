@@ -78,6 +78,9 @@ def _register_builtin() -> None:
     from ..models.gimupel import gimupel_spec
     from .gimupel import ARCHITECTURE as GIMUPEL, GimupelConfig
     register_architecture(Architecture(GIMUPEL, GimupelConfig.from_dict, gimupel_spec, lambda c: c.to_dict()))
+    from ..models.fidinex import fidinex_spec, refine_config as refine_fidinex
+    from .fidinex import ARCHITECTURE as FIDINEX, FidinexConfig
+    register_architecture(Architecture(FIDINEX, FidinexConfig.from_dict, fidinex_spec, lambda c: c.to_dict(), refine_fidinex))
 
 
 _register_builtin()

@@ -147,6 +147,7 @@ struct AttnParams {
     int chunk;                       // > 0: a query sees only the keys of its own chunk of this many positions
     int has_sink;                    // the softmax has one more score, without a value
     float sink_log2;                 // that score, in the units of scale_log2
+    const float* sinks;              // or a learned score per query head [H] (natural units); null: sink_log2 for all
     float out_scale;                 // factor on the result
     float scale_log2;
 };
@@ -276,8 +277,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant
         const int h = g * HG + r;
         if (p.n_splits == 1) {
             if (p.has_sink) {                     // the sink joins the denominator once, where the sums are complete
-                const float M2 = fmaxf(M, p.sink_log2), f = M == -INFINITY ? 0.f : exp2f(M - M2);
-                L = L * f + exp2f(p.sink_log2 - M2); O *= f;
+                const float sk = p.sinks ? p.sinks[h] * 1.4426950408889634f : p.sink_log2;
+                const float M2 = fmaxf(M, sk), f = M == -INFINITY ? 0.f : exp2f(M - M2);
+                L = L * f + exp2f(sk - M2); O *= f;
             }
             p.out[((size_t)tok * p.H + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L * p.out_scale : 0.f);
         } else {
@@ -290,8 +292,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant
 
 template <int HD>
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    bf16* __restrict__ out, int n_splits, int has_sink, float sink_log2, float out_scale) {
+                                    bf16* __restrict__ out, int n_splits, int has_sink, float sink_log2, float out_scale,
+                                    const float* __restrict__ sinks, int H) {
     const size_t th = blockIdx.x;                      // token * H + head
+    if (sinks) sink_log2 = sinks[th % H] * 1.4426950408889634f;
     pdl_wait();
     pdl_launch_dependents();
     const float* ml = part_ml + th * n_splits * 2;
@@ -404,9 +408,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constan
         l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
         l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
         if (p.has_sink) {
-            const float ma = fmaxf(m_a, p.sink_log2), mb = fmaxf(m_b, p.sink_log2);
+            const float sk = p.sinks ? p.sinks[h] * 1.4426950408889634f : p.sink_log2;
+            const float ma = fmaxf(m_a, sk), mb = fmaxf(m_b, sk);
             const float fa = m_a == -INFINITY ? 0.f : exp2f(m_a - ma), fb = m_b == -INFINITY ? 0.f : exp2f(m_b - mb);
-            l_a = l_a * fa + exp2f(p.sink_log2 - ma); l_b = l_b * fb + exp2f(p.sink_log2 - mb);
+            l_a = l_a * fa + exp2f(sk - ma); l_b = l_b * fb + exp2f(sk - mb);
 #pragma unroll
             for (int dt = 0; dt < Frag<HD>::DT; ++dt) { o[dt][0] *= fa; o[dt][1] *= fa; o[dt][2] *= fb; o[dt][3] *= fb; }
         }
@@ -477,7 +482,7 @@ extern "C" int tuff_attention_decode(const void* q, long long q_stride, const vo
                                      long long num_pages, const int* block_table, int max_blocks, const int* positions,
                                      const int* row_of_token, void* out, float* workspace, int n_splits, int* status,
                                      int n_tokens, int H, int G, int hd, int page_size, float scale, int window,
-                                     int chunk, int has_sink, float sink, float out_scale, cudaStream_t stream) {
+                                     int chunk, int has_sink, float sink, float out_scale, const float* sinks, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!supported(H, G, hd, page_size) || n_splits < 1) return TUFF_E_SIZE;
     if (((uintptr_t)q & 3) || (q_stride & 1) || ((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return TUFF_E_ALIGN;
@@ -489,7 +494,7 @@ extern "C" int tuff_attention_decode(const void* q, long long q_stride, const vo
     p.positions = positions; p.row_of_token = row_of_token; p.out = (bf16*)out; p.status = status;
     p.part_o = workspace; p.part_ml = workspace ? workspace + (size_t)n_tokens * H * n_splits * hd : nullptr;
     p.n_tokens = n_tokens; p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.n_splits = n_splits;
-    p.chunk = chunk; p.has_sink = has_sink; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
+    p.chunk = chunk; p.has_sink = (has_sink || sinks) ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.sinks = sinks; p.out_scale = out_scale;
     p.scale_log2 = scale * 1.4426950408889634f;
     if (n_splits > 1 && !workspace) return TUFF_E_SIZE;
     dim3 grid(n_tokens, G, n_splits);
@@ -507,8 +512,8 @@ extern "C" int tuff_attention_decode(const void* q, long long q_stride, const vo
         rc = launch_pdl(attn_decode_kernel<128>, grid, dim3(threads), smem, stream, mk, mv, p);
     }
     if (rc || (rc = launch_status()) || n_splits == 1) return rc;
-    if (hd == 64) rc = launch_pdl(attn_combine_kernel<64>, dim3(n_tokens * H), dim3(64), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, n_splits, has_sink, p.sink_log2, out_scale);
-    else rc = launch_pdl(attn_combine_kernel<128>, dim3(n_tokens * H), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, n_splits, has_sink, p.sink_log2, out_scale);
+    if (hd == 64) rc = launch_pdl(attn_combine_kernel<64>, dim3(n_tokens * H), dim3(64), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, n_splits, p.has_sink, p.sink_log2, out_scale, p.sinks, H);
+    else rc = launch_pdl(attn_combine_kernel<128>, dim3(n_tokens * H), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, n_splits, p.has_sink, p.sink_log2, out_scale, p.sinks, H);
     return rc ? rc : launch_status();
 }
 
@@ -516,7 +521,7 @@ extern "C" int tuff_attention_prefill(const void* q, long long q_stride, const v
                                       long long num_pages, const int* block_table, int max_blocks, const int* positions,
                                       const int* row_of_token, const int* cu_q, void* out, int* status, int n_tokens,
                                       int n_rows, int H, int G, int hd, int page_size, float scale, int window,
-                                      int chunk, int has_sink, float sink, float out_scale, cudaStream_t stream) {
+                                      int chunk, int has_sink, float sink, float out_scale, const float* sinks, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!supported(H, G, hd, page_size)) return TUFF_E_SIZE;
     if (((uintptr_t)q & 3) || (q_stride & 1) || ((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return TUFF_E_ALIGN;
@@ -527,7 +532,7 @@ extern "C" int tuff_attention_prefill(const void* q, long long q_stride, const v
     p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.max_blocks = max_blocks; p.n_pages = num_pages;
     p.positions = positions; p.row_of_token = row_of_token; p.cu_q = cu_q; p.out = (bf16*)out; p.status = status;
     p.n_tokens = n_tokens; p.n_rows = n_rows; p.H = H; p.G = G; p.page_size = page_size; p.window = window; p.n_splits = 1;
-    p.chunk = chunk; p.has_sink = has_sink; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
+    p.chunk = chunk; p.has_sink = (has_sink || sinks) ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.sinks = sinks; p.out_scale = out_scale;
     p.scale_log2 = scale * 1.4426950408889634f;
     const int HG = H / G, QTOK = 16 * (PRE_WARPS / HG);
     dim3 grid((n_tokens + QTOK - 1) / QTOK + n_rows, G);       // an upper bound on the blocks of all rows

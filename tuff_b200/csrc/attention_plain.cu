@@ -17,6 +17,11 @@
 // positions; the softmax may have a sink (a further score with no value) in its denominator; the
 // output may be scaled; values may have another width than keys (`vd`: the value heads then follow the
 // key heads in qkv with that width, their pages are [page][kv_head][slot][vd], and the output is [n, H*vd]).
+// Further: the sink may be a learned score per query head (`sinks`); a query may be multiplied, after its norm,
+// by a temperature that grows with its position, 1 + coef * ln(floor((pos + 1) / every) + 1); a value may be
+// blended with another layer's value of the same token before it is stored, (1 - lambda) v + lambda v_other;
+// and the values may be the leading `vd` elements of the keys themselves (`v_row`: the distance between two
+// value rows in elements, so that the key pages serve as value pages).
 //
 // The reference keeps one contiguous fp32 cache per sequence and is written for
 // head size 64; here the cache is paged ([page][kv_head][slot][hd], looked up
@@ -45,7 +50,9 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
                           const int* __restrict__ block_table, int max_blocks,
                           T* __restrict__ k_pages, T* __restrict__ v_pages,
                           int H, int G, int hd, int rot_dim, int page_size, float eps, int write_kv, Bounds bounds,
-                          int interleaved, float amplitude, const float* __restrict__ row_sumsq, int v_from_k, int vd) {
+                          int interleaved, float amplitude, const float* __restrict__ row_sumsq, int v_from_k, int vd,
+                          float q_temp_coef, int q_temp_every, const T* __restrict__ v_other, long long v_other_stride,
+                          const float* __restrict__ v_lambda) {
     constexpr int UNROLL = 4;                        // heads in flight per warp
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -53,6 +60,10 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
     pdl_launch_dependents();
     const int pos = ld_act(positions + t);
     const int r = ld_act(row_of_token + t);
+    // the query's temperature (1 when there is none), and the weight of the other layer's value
+    const float q_temp = q_temp_every > 0 ? 1.f + q_temp_coef * logf((float)((pos + 1) / q_temp_every) + 1.f) : 1.f;
+    const float lam = v_other ? v_lambda[0] : 0.f;
+    const T* vo = v_other ? v_other + (size_t)t * v_other_stride : nullptr;
     const bool v_sep = !v_from_k && vd != hd;        // values of another width: copied by a loop of their own
     const int n_heads = H + ((v_from_k || v_sep) ? G : 2 * G);
     const int half = rot_dim >> 1, n_pairs = hd >> 1;
@@ -127,14 +138,19 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
             if (!is_q && !is_k) {          // value head: copy to its page
                 if (write_kv) {
                     T* dst = v_pages + ((page_base + (head - H - G)) * page_size + in_page) * hd;
+                    const T* src = vo ? vo + (size_t)(head - H - G) * hd : nullptr;
 #pragma unroll
                     for (int i = 0; i < PPL; ++i)
-                        if (lane + 32 * i < n_pairs) { dst[e1[i]] = from_f32<T>(a[u][i]); dst[e2[i]] = from_f32<T>(b[u][i]); }
+                        if (lane + 32 * i < n_pairs) {
+                            float va = a[u][i], vb = b[u][i];
+                            if (src) { va = (1.f - lam) * va + lam * ld_act(src + e1[i]); vb = (1.f - lam) * vb + lam * ld_act(src + e2[i]); }
+                            dst[e1[i]] = from_f32<T>(va); dst[e2[i]] = from_f32<T>(vb);
+                        }
                 }
                 continue;
             }
             const bool normed = is_q ? q_norm_w != nullptr : k_norm_w != nullptr;
-            const float scale = !normed ? 1.f : row_sumsq ? (is_q ? whole_q : whole_k) : rsqrtf(ss[u] / (float)hd + eps);
+            const float scale = (!normed ? 1.f : row_sumsq ? (is_q ? whole_q : whole_k) : rsqrtf(ss[u] / (float)hd + eps)) * (is_q ? q_temp : 1.f);
             T* dst = (is_k && write_kv) ? k_pages + ((page_base + (head - H)) * page_size + in_page) * hd : nullptr;
             T* vdst = (is_k && write_kv && v_from_k) ? v_pages + ((page_base + (head - H)) * page_size + in_page) * hd : nullptr;
             const float* wcol = (normed && w_stride) ? (is_q ? q_norm_w + (size_t)head * hd : k_norm_w + (size_t)(head - H) * hd) : nullptr;
@@ -156,7 +172,11 @@ qk_norm_rope_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_norm_
         const T* vsrc = base + (size_t)(H + G) * hd;
         for (int g = blockIdx.y * QKV_WARPS + warp; g < G; g += stride) {
             T* dst = v_pages + ((page_base + g) * page_size + in_page) * vd;
-            for (int e = lane; e < vd; e += 32) dst[e] = from_f32<T>(ld_act(vsrc + (size_t)g * vd + e));
+            for (int e = lane; e < vd; e += 32) {
+                float v = ld_act(vsrc + (size_t)g * vd + e);
+                if (vo) v = (1.f - lam) * v + lam * ld_act(vo + (size_t)g * vd + e);
+                dst[e] = from_f32<T>(v);
+            }
         }
     }
 }
@@ -179,21 +199,24 @@ __global__ void qk_sumsq_kernel(const T* __restrict__ qkv, long long stride, int
 }
 
 constexpr int ATT_WARPS = 4;
-constexpr int MAX_PER_LANE = MAX_HD / 32;
+constexpr int WIDE_HD = 640;          // the widest key the attention kernel takes (keys that carry a latent and a rotated part)
 
-template <typename T>
+// MAX_PER_LANE: elements of a head per lane; 8 for heads up to 256, 20 for the wide ones
+template <typename T, int MAX_PER_LANE>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 paged_attention_plain_kernel(const T* __restrict__ q, long long q_stride, const T* __restrict__ k_pages,
                              const T* __restrict__ v_pages, const int* __restrict__ block_table,
                              int max_blocks, const int* __restrict__ positions,
                              const int* __restrict__ row_of_token, T* __restrict__ out,
                              int H, int G, int hd, int page_size, float scale, int window, Bounds bounds,
-                             int chunk, int has_sink, float sink, float out_scale, int vd) {
-    __shared__ float sh_acc[ATT_WARPS][MAX_HD];
+                             int chunk, int has_sink, float sink, float out_scale, int vd,
+                             const float* __restrict__ sinks, int v_row) {
+    __shared__ float sh_acc[ATT_WARPS][MAX_PER_LANE * 32];
     __shared__ float sh_m[ATT_WARPS], sh_l[ATT_WARPS];
     const int t = blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = h / (H / G);
+    if (sinks) { has_sink = 1; sink = sinks[h]; }      // a learned score per query head
     const int pos = positions[t];
     const int r = row_of_token[t];
     if (!check_row(bounds, r)) return;               // the same for the whole block
@@ -214,7 +237,7 @@ paged_attention_plain_kernel(const T* __restrict__ q, long long q_stride, const 
         const int page = bt[page_entry(j, page_size)];
         if (!check_page(bounds, page)) continue;
         const T* kp = k_pages + page_elem(page, g, page_offset(j, page_size), G, page_size, hd);
-        const T* vp = v_pages + page_elem(page, g, page_offset(j, page_size), G, page_size, vd);
+        const T* vp = v_pages + page_elem(page, g, page_offset(j, page_size), G, page_size, v_row);
         float s = 0.f;
 #pragma unroll
         for (int i = 0; i < MAX_PER_LANE; ++i) {
@@ -271,7 +294,8 @@ extern "C" int tuff_qk_norm_rope_write(void* qkv, int dtype, const float* q_norm
                                        int n_tokens, int H, int G, int hd, int rot_dim, int page_size,
                                        float eps, int write_kv, long long table_rows, long long n_pages, int* status,
                                        int interleaved, float amplitude, const float* row_sumsq, int v_from_k, int vd,
-                                       cudaStream_t stream) {
+                                       float q_temp_coef, int q_temp_every, const void* v_other, long long v_other_stride,
+                                       const float* v_lambda, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (vd <= 0) vd = hd;
     if (vd > MAX_HD) return TUFF_E_SIZE;
@@ -285,7 +309,8 @@ extern "C" int tuff_qk_norm_rope_write(void* qkv, int dtype, const float* q_norm
 #define QK_GO(T, PPL) return launch_pdl(qk_norm_rope_write_kernel<T, PPL>, grid, dim3(QKV_WARPS * 32), 0, stream, \
         (T*)qkv, q_norm_w, k_norm_w, inv_freq, positions, row_of_token, block_table, max_blocks, \
         (T*)k_pages, (T*)v_pages, H, G, hd, rot_dim, page_size, eps, write_kv, Bounds{table_rows, n_pages, status}, \
-        interleaved, amplitude, row_sumsq, v_from_k, vd)
+        interleaved, amplitude, row_sumsq, v_from_k, vd, q_temp_coef, q_temp_every, (const T*)v_other, v_other_stride, v_lambda)
+    if (v_other && (!v_lambda || v_from_k)) return TUFF_E_SIZE;
     if (dtype == TUFF_F32) {
         if (hd <= 64) QK_GO(float, 1); else if (hd <= 128) QK_GO(float, 2); else QK_GO(float, 4);
     } else if (dtype == TUFF_BF16) {
@@ -312,23 +337,22 @@ extern "C" int tuff_paged_attention_plain(const void* q, long long q_stride, con
                                           const int* positions, const int* row_of_token, void* out,
                                           int n_tokens, int H, int G, int hd, int page_size, float scale,
                                           int window, long long table_rows, long long n_pages, int* status,
-                                          int chunk, int has_sink, float sink, float out_scale, int vd, cudaStream_t stream) {
+                                          int chunk, int has_sink, float sink, float out_scale, int vd,
+                                          const float* sinks, int v_row, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (vd <= 0) vd = hd;
-    if (vd > MAX_HD) return TUFF_E_SIZE;
-    if (hd < 1 || hd > MAX_HD || G < 1 || H % G != 0 || page_size < 1 || H > 65535) return TUFF_E_SIZE;
+    if (v_row <= 0) v_row = vd;
+    if (vd > WIDE_HD) return TUFF_E_SIZE;
+    const bool wide = hd > MAX_HD || vd > MAX_HD;
+    if (hd < 1 || hd > WIDE_HD || G < 1 || H % G != 0 || page_size < 1 || H > 65535) return TUFF_E_SIZE;
     dim3 grid(n_tokens, H);
-    if (dtype == TUFF_F32)
-        paged_attention_plain_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
-            (const float*)q, q_stride, (const float*)k_pages, (const float*)v_pages, block_table, max_blocks,
-            positions, row_of_token, (float*)out, H, G, hd, page_size, scale, window, Bounds{table_rows, n_pages, status},
-            chunk, has_sink, sink, out_scale, vd);
-    else if (dtype == TUFF_BF16)
-        paged_attention_plain_kernel<bf16><<<grid, ATT_WARPS * 32, 0, stream>>>(
-            (const bf16*)q, q_stride, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_blocks,
-            positions, row_of_token, (bf16*)out, H, G, hd, page_size, scale, window, Bounds{table_rows, n_pages, status},
-            chunk, has_sink, sink, out_scale, vd);
-    else
-        return TUFF_E_DTYPE;
+#define ATT_GO(T, NPL) paged_attention_plain_kernel<T, NPL><<<grid, ATT_WARPS * 32, 0, stream>>>( \
+            (const T*)q, q_stride, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, \
+            positions, row_of_token, (T*)out, H, G, hd, page_size, scale, window, Bounds{table_rows, n_pages, status}, \
+            chunk, has_sink, sink, out_scale, vd, sinks, v_row)
+    if (dtype == TUFF_F32) { if (wide) ATT_GO(float, WIDE_HD / 32); else ATT_GO(float, MAX_HD / 32); }
+    else if (dtype == TUFF_BF16) { if (wide) ATT_GO(bf16, WIDE_HD / 32); else ATT_GO(bf16, MAX_HD / 32); }
+    else return TUFF_E_DTYPE;
+#undef ATT_GO
     return launch_status();
 }

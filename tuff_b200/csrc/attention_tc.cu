@@ -52,6 +52,7 @@ struct TcAttnParams {
     int n_rows, H, G, page_size, window, n_blocks;
     int chunk, has_sink;             // keys of the query's own chunk of positions only; one more score without a value
     float sink_log2, out_scale;      // that score in the units of scale_log2; factor on the result
+    const float* sinks;              // or a learned score per query head [H] (natural units); null: sink_log2 for all
     float scale_log2;
 };
 
@@ -326,7 +327,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
         tc_fence_after();
         if (ok && warp_valid) {
             // the sink's share, in the units of the row's reference maximum like l and O
-            if (p.has_sink && m_ref != -INFINITY) l += ex2(p.sink_log2 - m_ref * p.scale_log2);
+            if (p.has_sink && m_ref != -INFINITY) l += ex2((p.sinks ? p.sinks[h] * 1.4426950408889634f : p.sink_log2) - m_ref * p.scale_log2);
             const float inv = l > 0.f ? p.out_scale / l : 0.f;
             bf16* orow = p.out + ((size_t)(q0 + r) * p.H + h) * HD;
 #pragma unroll
@@ -374,7 +375,7 @@ extern "C" int tuff_attention_prefill_tc(const void* q, long long q_stride, cons
                                          long long num_pages, const int* block_table, int max_blocks, const int* positions,
                                          const int* cu_q, void* out, int* status, int n_tokens, int n_rows, int H, int G,
                                          int hd, int page_size, float scale, int window, int chunk, int has_sink,
-                                         float sink, float out_scale, cudaStream_t stream) {
+                                         float sink, float out_scale, const float* sinks, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!supported(H, G, hd, page_size)) return TUFF_E_SIZE;
     if (((uintptr_t)q & 15) || (q_stride & 7) || ((uintptr_t)out & 15) || ((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127))
@@ -386,7 +387,7 @@ extern "C" int tuff_attention_prefill_tc(const void* q, long long q_stride, cons
     p.q = (const bf16*)q; p.q_stride = q_stride; p.block_table = block_table; p.max_blocks = max_blocks; p.n_pages = num_pages;
     p.positions = positions; p.cu_q = cu_q; p.out = (bf16*)out; p.status = status;
     p.n_rows = n_rows; p.H = H; p.G = G; p.page_size = page_size; p.window = window;
-    p.chunk = chunk; p.has_sink = has_sink; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
+    p.chunk = chunk; p.has_sink = (has_sink || sinks) ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.sinks = sinks; p.out_scale = out_scale;
     p.n_blocks = (n_tokens + QROWS - 1) / QROWS + n_rows;      // an upper bound on the blocks of all requests
     p.scale_log2 = scale * 1.4426950408889634f;
     const int smem = Smem<64>::TOTAL;

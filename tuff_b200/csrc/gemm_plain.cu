@@ -18,7 +18,10 @@ constexpr int BM = 64, BN = 64, BK = 16, PAD = 4;
 template <typename AT, typename WT, typename CT, bool ACCUM>
 __global__ void __launch_bounds__(256)
 gemm_plain_kernel(const AT* __restrict__ A, const WT* __restrict__ W, CT* __restrict__ C,
-                  int M, int N, int K, long long lda, long long ldw, long long ldc) {
+                  int M, int N, int K, long long lda, long long ldw, long long ldc,
+                  long long sa, long long sw, long long sc) {
+    // blockIdx.z: which product of a batch (one per head, say); the strides between them in elements
+    A += (size_t)blockIdx.z * sa; W += (size_t)blockIdx.z * sw; C += (size_t)blockIdx.z * sc;
     __shared__ float As[BK][BM + PAD];
     __shared__ float Ws[BK][BN + PAD];
     const int tid = threadIdx.x;
@@ -73,14 +76,18 @@ gemm_plain_kernel(const AT* __restrict__ A, const WT* __restrict__ W, CT* __rest
 }
 }  // namespace
 
-extern "C" int tuff_gemm_plain(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
-                               int M, int N, int K, long long lda, long long ldw, long long ldc,
-                               int accumulate, cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return 0;
-    if (K <= 0) return TUFF_E_SIZE;
-    dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
+// `batch` products in one launch: product b reads A + b*sa, W + b*sw and writes C + b*sc (strides in elements).
+// The heads of a projection that has a matrix of its own per head are such a batch: A [M, heads, K] with
+// lda = heads*K and sa = K, and so on.
+extern "C" int tuff_gemm_plain_batched(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
+                                       int M, int N, int K, long long lda, long long ldw, long long ldc,
+                                       int batch, long long sa, long long sw, long long sc,
+                                       int accumulate, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    if (K <= 0 || batch > 65535) return TUFF_E_SIZE;
+    dim3 grid(ceil_div(N, BN), ceil_div(M, BM), batch);
 #define GO(AT, WT, CT, ACC) gemm_plain_kernel<AT, WT, CT, ACC><<<grid, 256, 0, stream>>>( \
-        (const AT*)A, (const WT*)W, (CT*)C, M, N, K, lda, ldw, ldc)
+        (const AT*)A, (const WT*)W, (CT*)C, M, N, K, lda, ldw, ldc, sa, sw, sc)
     if (accumulate && c_dtype != TUFF_F32) return TUFF_E_DTYPE;
     if (a_dtype == TUFF_F32 && w_dtype == TUFF_F32 && c_dtype == TUFF_F32) {
         if (accumulate) GO(float, float, float, true); else GO(float, float, float, false);
@@ -95,4 +102,10 @@ extern "C" int tuff_gemm_plain(const void* A, int a_dtype, const void* W, int w_
     }
 #undef GO
     return launch_status();
+}
+
+extern "C" int tuff_gemm_plain(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
+                               int M, int N, int K, long long lda, long long ldw, long long ldc,
+                               int accumulate, cudaStream_t stream) {
+    return tuff_gemm_plain_batched(A, a_dtype, W, w_dtype, C, c_dtype, M, N, K, lda, ldw, ldc, 1, 0, 0, 0, accumulate, stream);
 }

@@ -208,6 +208,60 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: 
                                c_longlong(out.stride(0)), c_int(1 if accumulate else 0), _stream()), "gemm_plain")
 
 
+def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """A projection with a matrix of its own per head: out[t, h, :] = w[h] @ a[t, h, :], for a [T, H, K] and
+    out [T, H, N] (views whose last dimension is contiguous and whose head stride is any number of
+    elements) and w [H, N, K] contiguous.  FFMA with fp32 sums in ascending k, all heads in one launch."""
+    _written(out)
+    T, H, K = a.shape
+    N = w.shape[1]
+    assert w.shape == (H, N, K) and out.shape == (T, H, N) and a.stride(2) == 1 and out.stride(2) == 1
+    _contig(w, "w")
+    lib = load_library("gemm_plain")
+    _check(lib.tuff_gemm_plain_batched(_ptr(a), dtype_code(a), _ptr(w), dtype_code(w), _ptr(out), dtype_code(out),
+                                       c_int(T), c_int(N), c_int(K), c_longlong(a.stride(0)), c_longlong(K),
+                                       c_longlong(out.stride(0)), c_int(H), c_longlong(a.stride(1)), c_longlong(N * K),
+                                       c_longlong(out.stride(1)), c_int(0), _stream()), "head_linear")
+
+
+def relu2(z: torch.Tensor) -> None:
+    """z <- max(z, 0)^2 in place."""
+    _written(z)
+    _contig(z, "z")
+    lib = load_library("hyper")
+    _check(lib.tuff_relu2(_ptr(z), dtype_code(z), c_longlong(z.numel()), _stream()), "relu2")
+
+
+def hc_step(X: torch.Tensor, *, x_init: torch.Tensor | None = None, y: torch.Tensor | None = None,
+            mix: torch.Tensor | None = None, out_w: torch.Tensor | None = None, in_w: torch.Tensor | None = None,
+            norm_w: torch.Tensor | None = None, eps: float = 0.0, h_out: torch.Tensor | None = None,
+            u_out: torch.Tensor | None = None, zero_y: bool = True) -> None:
+    """One step of a model with several residual streams X [S, T, d] (fp32).  First the streams change: every
+    stream becomes `x_init` [T, d]; or, all at once from the old ones, X_t <- sum_s mix[s, t] X_s + out_w[t] * y
+    (y [T, d] is then cleared if `zero_y`); or not at all.  Then u = sum_t in_w[t] X_t (in_w None: the plain
+    sum) is read out: `u_out` gets u, `h_out` gets u * rsqrt(mean(u^2) + eps) * norm_w in its own dtype
+    (norm_w None: u itself)."""
+    S, T, d = X.shape
+    assert X.dtype == torch.float32
+    _contig(X, "X"); _written(X)
+    for t_, shape in ((x_init, (T, d)), (y, (T, d)), (mix, (S, S)), (out_w, (S,)), (in_w, (S,)), (norm_w, (d,)), (u_out, (T, d))):
+        if t_ is not None:
+            assert t_.dtype == torch.float32 and tuple(t_.shape) == shape, (t_.shape, shape)
+            _contig(t_, "hc_step operand")
+    if h_out is not None:
+        assert tuple(h_out.shape) == (T, d)
+        _contig(h_out, "h_out"); _written(h_out)
+    if u_out is not None:
+        _written(u_out)
+    if y is not None:
+        _written(y)
+    lib = load_library("hyper")
+    _check(lib.tuff_hc_step(_ptr(X), c_int(S), c_int(T), c_int(d), _ptr(x_init), _ptr(y), _ptr(mix), _ptr(out_w),
+                            _ptr(in_w), _ptr(norm_w), c_float(eps), _ptr(h_out),
+                            c_int(dtype_code(h_out) if h_out is not None else F32), _ptr(u_out),
+                            c_int(1 if zero_y else 0), _stream()), "hc_step")
+
+
 _tc_state: dict = {}
 
 
@@ -515,6 +569,12 @@ def linear_swiglu(a, w13: torch.Tensor, out: torch.Tensor, block: int = 0) -> No
     swiglu(gu, out, block)
 
 
+def linear_relu2(a, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = max(a @ w.T, 0)^2; `a` may be a NormedRows."""
+    linear(a, w, out)
+    relu2(out)
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """out (=|+=) a @ w.T, by the kernel that suits the element types and the shape:
     bf16 operands that meet TMA's alignment rules go to the tensor cores, everything else
@@ -583,8 +643,13 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_norm_w: torch.Tensor | None, k_norm_
                        block_table: torch.Tensor | None, k_pages: torch.Tensor | None,
                        v_pages: torch.Tensor | None, H: int, G: int, hd: int, rot_dim: int, eps: float,
                        write_kv: bool = True, interleaved: bool = False, amplitude: float = 1.0,
-                       whole_norm: bool = False, v_from_k: bool = False, v_head_dim: int | None = None) -> None:
+                       whole_norm: bool = False, v_from_k: bool = False, v_head_dim: int | None = None,
+                       q_temp: tuple | None = None, v_other: torch.Tensor | None = None,
+                       v_lambda: torch.Tensor | None = None) -> None:
     """RMSNorm + rotation of q and k in place; K and V stored in their pages.
+    `q_temp` = (coef, every): after its norm a query is multiplied by 1 + coef * ln(floor((pos + 1) / every) + 1).
+    `v_other` [n, G * value width] (last dimension contiguous) with `v_lambda` (one fp32 on the device): the value
+    stored is (1 - lambda) v + lambda v_other.
 
     k_pages / v_pages: [num_pages, G, page_size, hd]; block_table: [rows, max_blocks] int32.
     The norm is per head with a weight [hd], or (`whole_norm`) over a token's whole q projection and whole
@@ -609,6 +674,11 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_norm_w: torch.Tensor | None, k_norm_
         page_size, max_blocks = k_pages.shape[2], block_table.shape[1]
     if rot_dim:
         assert inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2
+    if v_other is not None:
+        assert write_kv and not v_from_k and v_other.shape == (n, G * vd) and v_other.stride(1) == 1 and v_other.dtype == qkv.dtype
+        assert v_lambda is not None and v_lambda.dtype == torch.float32 and v_lambda.numel() == 1
+    if q_temp:
+        assert int(q_temp[1]) >= 1
     for wv, heads in ((q_norm_w, H), (k_norm_w, G)):
         assert wv is None or (wv.dtype == torch.float32 and wv.numel() == (heads * hd if whole_norm else hd))
     lib = load_library("attention_plain")
@@ -625,16 +695,45 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_norm_w: torch.Tensor | None, k_norm_
                                        c_longlong(block_table.shape[0] if write_kv else 0),
                                        c_longlong(k_pages.shape[0] if write_kv else 0), _ptr(status_word(qkv.device)),
                                        c_int(1 if interleaved else 0), c_float(amplitude), _ptr(sumsq),
-                                       c_int(1 if v_from_k else 0), c_int(vd), _stream()), "qk_norm_rope_write")
+                                       c_int(1 if v_from_k else 0), c_int(vd),
+                                       c_float(q_temp[0] if q_temp else 0.0), c_int(q_temp[1] if q_temp else 0),
+                                       _ptr(v_other), c_longlong(v_other.stride(0) if v_other is not None else 0),
+                                       _ptr(v_lambda), _stream()), "qk_norm_rope_write")
+
+
+def latent_prepare(qd: torch.Tensor, ql: torch.Tensor, c_norm_w: torch.Tensor, inv_freq: torch.Tensor,
+                   positions: torch.Tensor, row_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
+                   H: int, dim: int, rd: int, rank: int, rot_dims: int, eps: float, write_kv: bool = True) -> None:
+    """For attention over a latent cache.  qd [n, H*(dim+rd) + rank + rd] is the stacked projection
+    [query heads (plain | rotated) | c | kr].  Stores rmsnorm(c) * c_norm_w and the rotated kr as the token's row
+    [c | kr] of k_pages [pages, 1, page_size, rank + rd], and the rotated query parts in ql[:, :, rank:]
+    (ql [n, H, rank + rd]; its first `rank` columns per head are left for the absorbed plain parts)."""
+    n = qd.shape[0]
+    assert qd.shape[1] == H * (dim + rd) + rank + rd and qd.stride(1) == 1 and ql.shape == (n, H, rank + rd)
+    assert qd.dtype == ql.dtype == k_pages.dtype and k_pages.shape[1] == 1 and k_pages.shape[3] == rank + rd
+    assert c_norm_w.dtype == torch.float32 and c_norm_w.numel() == rank
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2
+    _contig(ql, "ql"); _contig(k_pages, "k_pages"); _contig(block_table, "block_table")
+    _i32(positions, "positions"); _i32(row_of_token, "row_of_token"); _i32(block_table, "block_table")
+    _written(ql)
+    lib = load_library("latent_attention")
+    _check(lib.tuff_latent_prepare(_ptr(qd), c_longlong(qd.stride(0)), _ptr(ql), dtype_code(qd), _ptr(c_norm_w),
+                                   _ptr(inv_freq), _ptr(positions), _ptr(row_of_token), _ptr(block_table),
+                                   c_int(block_table.shape[1]), _ptr(k_pages), c_int(n), c_int(H), c_int(dim), c_int(rd),
+                                   c_int(rank), c_int(rot_dims), c_int(k_pages.shape[2]), c_float(eps),
+                                   c_int(1 if write_kv else 0), c_longlong(block_table.shape[0]),
+                                   c_longlong(k_pages.shape[0]), _ptr(status_word(qd.device)), _stream()), "latent_prepare")
 
 
 def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                           positions: torch.Tensor, row_of_token: torch.Tensor, out: torch.Tensor, H: int, G: int,
-                          hd: int, scale: float, window: int = 0, chunk: int = 0, sink: float | None = None,
-                          out_scale: float = 1.0, v_head_dim: int | None = None) -> None:
+                          hd: int, scale: float, window: int = 0, chunk: int = 0, sink=None,
+                          out_scale: float = 1.0, v_head_dim: int | None = None, values_in_keys: bool = False) -> None:
     """Causal attention of each token over its request's cached keys (the last `window` if > 0; only
     those of its own chunk of `chunk` positions if > 0).  `sink`: a further score without a value in the
-    softmax's denominator.  The result is multiplied by `out_scale`.
+    softmax's denominator: a number, or an fp32 tensor [H] with a learned score per query head.  The result is
+    multiplied by `out_scale`.  `values_in_keys`: a value is the first `v_head_dim` elements of its key
+    (`v_pages` is not read).
 
     q: [n, >= H*hd] (row stride taken from the tensor), out: [n, H*vd] with vd = `v_head_dim` (default hd),
     the width of the value pages.
@@ -642,7 +741,16 @@ def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
     n = q.shape[0]
     vd = hd if v_head_dim is None else int(v_head_dim)
     assert q.stride(1) == 1 and out.shape == (n, H * vd) and q.dtype == k_pages.dtype == out.dtype
-    assert v_pages.shape[3] == vd and k_pages.shape[3] == hd
+    assert k_pages.shape[3] == hd
+    sinks = sink if isinstance(sink, torch.Tensor) else None
+    if sinks is not None:
+        assert sinks.dtype == torch.float32 and sinks.numel() == H
+        _contig(sinks, "sinks")
+        sink = 0.0
+    if values_in_keys:
+        assert vd <= hd
+        v_pages = k_pages
+    assert v_pages.shape[3] == (hd if values_in_keys else vd)
     _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages"); _contig(block_table, "block_table")
     _i32(block_table, "block_table"); _i32(positions, "positions"); _i32(row_of_token, "row_of_token")
     lib = load_library("attention_plain")
@@ -652,7 +760,8 @@ def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
                                           c_int(G), c_int(hd), c_int(k_pages.shape[2]), c_float(scale),
                                           c_int(window), c_longlong(block_table.shape[0]), c_longlong(k_pages.shape[0]),
                                           _ptr(status_word(q.device)), c_int(chunk or 0), c_int(0 if sink is None else 1),
-                                          c_float(0.0 if sink is None else sink), c_float(out_scale), c_int(vd), _stream()),
+                                          c_float(0.0 if sink is None else sink), c_float(out_scale), c_int(vd),
+                                          _ptr(sinks), c_int(hd if values_in_keys else vd), _stream()),
            "paged_attention_plain")
 
 
@@ -700,7 +809,13 @@ def attention_flash_supported(q: torch.Tensor, k_pages: torch.Tensor, H: int, G:
 
 
 def _attn_opts(chunk, sink, out_scale):
-    return (c_int(chunk or 0), c_int(0 if sink is None else 1), c_float(0.0 if sink is None else sink), c_float(out_scale))
+    """chunk, whether there is a sink, its score when it is one number, the output scale, and the learned scores
+    per query head when `sink` is an fp32 tensor [H]."""
+    if isinstance(sink, torch.Tensor):
+        assert sink.dtype == torch.float32 and sink.is_contiguous()
+        return (c_int(chunk or 0), c_int(1), c_float(0.0), c_float(out_scale), _ptr(sink))
+    return (c_int(chunk or 0), c_int(0 if sink is None else 1), c_float(0.0 if sink is None else sink), c_float(out_scale),
+            c_void_p(0))
 
 
 def attention_decode(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale,
@@ -773,7 +888,8 @@ def attention_prefill_tc(q, k_pages, v_pages, block_table, positions, cu_q, out,
 def paged_attention(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale,
                     window: int = 0, ctx=None, cu_q=None, all_single: bool | None = None,
                     max_seq_len: int | None = None, single_prefix: int | None = None, chunk: int = 0,
-                    sink: float | None = None, out_scale: float = 1.0, v_head_dim: int | None = None) -> None:
+                    sink=None, out_scale: float = 1.0, v_head_dim: int | None = None,
+                    values_in_keys: bool = False) -> None:
     """Attention over the paged cache by the kernel that suits the batch: the tensor-core kernels
     for bf16 with head size 64 or 128 (the sliced one for rows that bring a single token, the
     blocked ones for portions of prompts), the plain kernel for everything else.  `single_prefix`:
@@ -784,10 +900,11 @@ def paged_attention(q, k_pages, v_pages, block_table, positions, row_of_token, o
         all_single = ctx.all_single if all_single is None else all_single
         max_seq_len = ctx.max_seq_len if max_seq_len is None else max_seq_len
         single_prefix = ctx.single_prefix if single_prefix is None else single_prefix
-    if v_head_dim is not None and int(v_head_dim) != hd:
+    if (v_head_dim is not None and int(v_head_dim) != hd) or values_in_keys:
         # values of another width than keys: the plain kernel (the tensor-core kernels take equal widths)
         paged_attention_plain(q, k_pages, v_pages, block_table, positions, row_of_token, out, H, G, hd, scale, window,
-                              chunk=chunk, sink=sink, out_scale=out_scale, v_head_dim=v_head_dim)
+                              chunk=chunk, sink=sink, out_scale=out_scale, v_head_dim=v_head_dim,
+                              values_in_keys=values_in_keys)
         return
     assert q.stride(1) == 1 and out.shape == (q.shape[0], H * hd) and q.dtype == k_pages.dtype == out.dtype
     opts = dict(chunk=chunk, sink=sink, out_scale=out_scale)

@@ -66,7 +66,8 @@ class Model:
     def bind_weights(self, tensors: Dict[str, torch.Tensor], act_dtype: torch.dtype) -> None:
         self.act_dtype = act_dtype
         for part, ps in self._bound:
-            local = {l: tensors[ps.tensors[l]] for l in part.weight_decls()}
+            local = {l: tensors[ps.tensors[l]] for l, decl in part.weight_decls().items()
+                     if not (decl.optional and ps.tensors[l] not in tensors)}
             part.bind(local, act_dtype)
 
     def reserve(self, device, max_rows: int, max_context: int) -> None:
@@ -118,4 +119,6 @@ class Model:
                 layer.block.forward(ctx, x, layer, storages[e.storage], e.reads_only, next_norm=nxt)
             else:
                 layer.block.forward(ctx, x, layer, storages[e.storage], e.reads_only)
+        if self.schedule:
+            x = self.layers[self.schedule[-1].layer].block.finish(ctx, x)
         return self.head.forward(ctx, x, self.final_norm)

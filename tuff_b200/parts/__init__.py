@@ -4,4 +4,5 @@ from .base import (BLOCKS, CompositeNeed, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXE
                    FeedForward, Head, Mixer, Norm, PagedKVNeed, Part, PartSpec, PositionEncoding, StateNeed,
                    WeightDecl, register_block, register_embedding, register_feed_forward, register_head,
                    register_mixer, register_norm, register_position_encoding)
-from . import attention, block, embedding, ffn, linear_attention, moe, norm, parallel, rope, shortconv, ssm  # noqa: F401  (registration)
+from . import (attention, block, embedding, ffn, hyper, latent_attention, linear_attention, moe, norm, parallel, rope,  # noqa: F401
+               shortconv, ssm)  # noqa: F401  (registration)

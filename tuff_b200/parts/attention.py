@@ -19,7 +19,12 @@ score s without a value to every softmax (s = 0: one is added to the denominator
 projection (a branch's weight in a sum of mixers); `v_head_dim` gives values another
 width than keys (the output projection then reads H * v_head_dim columns);
 `qk_norm_weight=False` norms q and k without a learned weight (each head divided by
-its root mean square and nothing else).
+its root mean square and nothing else); `sink="learned"` takes the sink's score from a
+weight with one number per query head; `q_temp=(coef, every)` multiplies a query, after
+its norm, by 1 + coef * ln(floor((pos + 1) / every) + 1); `v_mix` blends values across
+layers: the layer with `v_mix="source"` leaves its values as projected (one per token of
+the step) under `v_mix_key` for the layers that follow, and a layer with `v_mix="blend"`
+stores (1 - lambda) v + lambda v_source, lambda being its weight `vmix` (one number).
 """
 from __future__ import annotations
 
@@ -39,7 +44,9 @@ class GQAAttention(Mixer):
                  qk_norm_eps: float | None = None, position_encoding: PartSpec | dict | None = None,
                  window: int | None = None, scale: float | None = None, qk_norm_span: str = "head",
                  values: str = "projection", chunk: int | None = None, sink: float | None = None,
-                 out_scale: float = 1.0, v_head_dim: int | None = None, qk_norm_weight: bool = True):
+                 out_scale: float = 1.0, v_head_dim: int | None = None, qk_norm_weight: bool = True,
+                 q_temp: tuple | list | None = None, v_mix: str | None = None, v_mix_key: str = "v_mix",
+                 unused_vmix_weight: bool = False):
         self.d, self.H, self.G, self.hd = int(d_model), int(num_heads), int(num_kv_heads), int(head_dim)
         self.vd = self.hd if not v_head_dim else int(v_head_dim)
         self.norm_weight = bool(qk_norm_weight)
@@ -50,7 +57,14 @@ class GQAAttention(Mixer):
         if self.v_from_k and self.vd != self.hd:
             raise ValueError("gqa_attention: values='keys' leaves no room for a value width of its own")
         self.chunk = None if not chunk else int(chunk)
-        self.sink = None if sink is None else float(sink)
+        self.learned_sink = sink == "learned"
+        self.sink = None if (sink is None or self.learned_sink) else float(sink)
+        self.q_temp = None if not q_temp else (float(q_temp[0]), int(q_temp[1]))
+        if self.q_temp is not None and self.q_temp[1] < 1:
+            raise ValueError(f"gqa_attention: q_temp every = {self.q_temp[1]} must be at least 1")
+        if v_mix not in (None, "source", "blend"):
+            raise ValueError(f"gqa_attention: v_mix {v_mix!r}; choose source or blend")
+        self.v_mix, self.v_mix_key, self.unused_vmix = v_mix, str(v_mix_key), bool(unused_vmix_weight)
         self.out_scale = float(out_scale)
         if self.H % self.G:
             raise ValueError(f"num_heads {self.H} is not a multiple of num_kv_heads {self.G}")
@@ -67,6 +81,14 @@ class GQAAttention(Mixer):
                  "v_proj": WeightDecl((G * self.vd, d)), "out_proj": WeightDecl((d, H * self.vd))}
         if self.v_from_k:
             del decls["v_proj"]
+            if self.v_mix:
+                raise ValueError("gqa_attention: values='keys' has no values of its own to blend")
+        if self.learned_sink:
+            decls["sink"] = WeightDecl((H,), role="vector")
+        if self.v_mix:                       # the source layer's checkpoint carries the number too, unused
+            decls["vmix"] = WeightDecl((), role="vector")
+        elif self.unused_vmix:
+            decls["vmix"] = WeightDecl((), role="vector", optional=True)
         if self.qk_norm_eps is not None and not self.norm_weight:
             if self.whole_norm:
                 raise ValueError("gqa_attention: a norm over the whole projection has a weight")
@@ -96,6 +118,8 @@ class GQAAttention(Mixer):
         if self.qk_norm_eps is not None and not self.norm_weight:
             # the kernel norms the heads it has a weight for: ones leave the unit root mean square as it is
             self.qn = self.kn = torch.ones(self.hd, dtype=torch.float32, device=self.wo.device)
+        self.sinks = weights["sink"].contiguous() if self.learned_sink else None
+        self.lam = weights["vmix"].reshape(1).contiguous() if self.v_mix == "blend" else None
         self.w = {"out_proj": self.wo}
 
     def forward(self, ctx, cache, h, residual, reads_only=False):
@@ -106,7 +130,17 @@ class GQAAttention(Mixer):
             raise ValueError("gqa_attention with a norm over the whole projection cannot run on another layer's cache")
         qkv = torch.empty((T, (H + g_here) * hd + (0 if self.v_from_k else g_here * vd)), dtype=self.act_dtype, device=h.device)
         ops.linear(h, self.wq if reads_only else self.wqkv, qkv)
-        opts = dict(whole_norm=self.whole_norm, v_from_k=self.v_from_k and not reads_only, v_head_dim=vd)
+        opts = dict(whole_norm=self.whole_norm, v_from_k=self.v_from_k and not reads_only, v_head_dim=vd, q_temp=self.q_temp)
+        if self.v_mix and not reads_only:
+            v_here = qkv[:, (H + G) * hd:]
+            if self.v_mix == "source":
+                ctx.extra[self.v_mix_key] = v_here           # stays as projected: the kernel below only copies it
+            else:
+                src = ctx.extra.get(self.v_mix_key)
+                if src is None or src.shape != v_here.shape:
+                    raise ValueError("gqa_attention: v_mix='blend' needs an earlier layer of the step with "
+                                     "v_mix='source' and values of the same shape")
+                opts.update(v_other=src, v_lambda=self.lam)
         table = ctx.block_tables[cache.group]
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
         fused = self.pos.fused_tables(qkv.device) if (self.pos is not None and hasattr(self.pos, "fused_tables")) else None
@@ -121,15 +155,18 @@ class GQAAttention(Mixer):
             if self.v_from_k:
                 raise ValueError("gqa_attention: values='keys' needs a position encoding with fused tables (or none)")
             ops.qk_norm_rope_write(qkv, self.qn, self.kn, None, ctx.positions, ctx.row_of_token, None, None, None,
-                                   H, g_here, hd, 0, eps, write_kv=False, whole_norm=self.whole_norm, v_head_dim=vd)
+                                   H, g_here, hd, 0, eps, write_kv=False, whole_norm=self.whole_norm, v_head_dim=vd,
+                                   q_temp=self.q_temp)
             q3 = qkv[:, : H * hd].unflatten(1, (H, hd))
             k3 = None if reads_only else qkv[:, H * hd:(H + G) * hd].unflatten(1, (G, hd))
             self.pos.rotate(ctx, q3, k3)
             if not reads_only:
                 ops.qk_norm_rope_write(qkv, None, None, None, ctx.positions, ctx.row_of_token, table,
-                                       cache.k_pages, cache.v_pages, H, G, hd, 0, 0.0, write_kv=True, v_head_dim=vd)
+                                       cache.k_pages, cache.v_pages, H, G, hd, 0, 0.0, write_kv=True, v_head_dim=vd,
+                                       v_other=opts.get("v_other"), v_lambda=opts.get("v_lambda"))
         att = torch.empty((T, H * vd), dtype=self.act_dtype, device=qkv.device)
         ops.paged_attention(qkv, cache.k_pages, cache.v_pages, table, ctx.positions, ctx.row_of_token, att,
-                            H, G, hd, self.scale, self.window or 0, ctx=ctx, chunk=self.chunk or 0, sink=self.sink,
+                            H, G, hd, self.scale, self.window or 0, ctx=ctx, chunk=self.chunk or 0,
+                            sink=self.sinks if self.learned_sink else self.sink,
                             out_scale=self.out_scale, v_head_dim=vd)
         ops.linear(att, self.wo, residual, accumulate=True)

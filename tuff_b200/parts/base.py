@@ -19,6 +19,8 @@ Interfaces (ctx is the step's `StepContext`):
   FeedForward.forward(ctx, h, residual)                residual += ffn(h)
   PositionEncoding.rotate(ctx, q, k) or fused_tables() see parts/rope.py
   Block.forward(ctx, x, layer, cache, reads_only, next_norm=None)   runs one layer on the residual x
+  Block.finish(ctx, x) -> x                            after the last layer: a block that keeps the stream in a
+                                                       form of its own (several streams) folds it back
   Embedding.forward(ctx) -> x                          fp32 [T, d]
   Head.forward(ctx, x, norm) -> logits                 fp32 [n_wanted, vocab]
 """
@@ -44,6 +46,7 @@ class WeightDecl:
     shape: Tuple[int, ...]
     role: str = "matrix"
     init: str = "normal"
+    optional: bool = False     # a checkpoint may leave it out (a tensor that a layer's options make unused)
 
 
 @dataclass(frozen=True)
@@ -58,6 +61,7 @@ class PagedKVNeed:
     window: int | None = None
     v_head_dim: int | None = None
     chunk: int | None = None
+    values_in_keys: bool = False   # the values are leading elements of the keys: there are no value pages
 
 
 @dataclass(frozen=True)
@@ -137,6 +141,11 @@ class Block(Part):
         """`next_norm`: the norm that reads x after this layer (the next layer's first norm, or the
         final norm), if the caller knows it; a block may `announce` x to it before its last write."""
         raise NotImplementedError
+
+    def finish(self, ctx, x):
+        """Called once after the last layer ran, with the stream the layers were given; returns the stream
+        [T, d] that the final norm reads.  A block that keeps more than x between layers folds it back here."""
+        return x
 
 
 class Embedding(Part):

@@ -34,3 +34,19 @@ class SwiGLU(FeedForward):
         act = torch.empty((T, self.F), dtype=self.act_dtype, device=h.device)
         ops.linear_swiglu(h, self.w13, act, self.w13_block)
         ops.linear(act, self.w2, residual, accumulate=True)
+
+
+@register_feed_forward("relu2_mlp")
+class ReluSquaredMlp(FeedForward):
+    """A feed-forward without a gate: out = W_down max(W_up h, 0)^2, added to the residual."""
+
+    def __init__(self, d_model: int, ffn_dim: int):
+        self.d, self.F = int(d_model), int(ffn_dim)
+
+    def weight_decls(self):
+        return {"up": WeightDecl((self.F, self.d)), "down": WeightDecl((self.d, self.F))}
+
+    def forward(self, ctx, h, residual):
+        act = torch.empty((h.shape[0], self.F), dtype=self.act_dtype, device=h.device)
+        ops.linear_relu2(h, self.w["up"], act)
+        ops.linear(act, self.w["down"], residual, accumulate=True)

@@ -59,7 +59,7 @@ def load_checkpoint(model_dir: str, expected: Dict[str, WeightDecl], engine_dtyp
     files = ModelFiles(model_dir)
     try:
         have = files.entries
-        missing = sorted(n for n in expected if n not in have)
+        missing = sorted(n for n in expected if n not in have and not expected[n].optional)
         unexpected = sorted(n for n in have if n not in expected)
         wrong_shape, wrong_dtype = [], []
         for n, decl in expected.items():
@@ -73,6 +73,8 @@ def load_checkpoint(model_dir: str, expected: Dict[str, WeightDecl], engine_dtyp
             raise WeightError(model_dir, missing, unexpected, wrong_shape, wrong_dtype)
         out: Dict[str, torch.Tensor] = {}
         for n, decl in expected.items():
+            if n not in have:
+                continue                  # optional and absent
             host = convert_for_role(files.tensor(n), decl, engine_dtype)
             out[n] = host.to(device)
         return out
