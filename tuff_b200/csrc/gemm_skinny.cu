@@ -62,7 +62,7 @@ constexpr int MAX_SPLITS = 8;      // the portable cluster size
 #define SKINNY_CH 16               // accumulator columns read from tensor memory and sent to their owners at a time
 #endif
 
-enum : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+enum : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_RELU2 = 4 };
 
 struct SkinnyParams {
     void* out;                 // [M, ldc] bf16 or fp32
@@ -380,6 +380,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                             for (int j = 0; j < 4; ++j) if (col[k] + j < p.n_out) xw[j] = __float2bfloat16_rn(e[j]);
                         }
                     }
+                } else if (p.epi == EPI_RELU2) {
+                    // the product rounded to bf16 first, as a separate projection would store it, then max(., 0)^2
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float z = fmaxf(bf16_round(v[k][j] * sc[k]), 0.f);
+                        r[j] = z * z;
+                    }
                 } else {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) r[j] = v[k][j] * sc[k];
@@ -522,7 +529,7 @@ extern "C" int tuff_gemm_skinny_ctas(int M, int w_rows, int K, int epilogue) {
 
 // C[M, n_out] (=|+=) A[M,K] W[w_rows,K]^T for M <= 128; bf16 A and W.  epilogue 0: store (C bf16 or
 // fp32, n_out = w_rows); 1: C += (fp32); 2 (M <= 64): W = gate and up rows in alternating blocks of 128, C bf16
-// [M, w_rows / 2] = silu(gate) * up.  emit_w / emit_xw / emit_part (epilogue 1, may be null): see the
+// [M, w_rows / 2] = silu(gate) * up; 4: C bf16 = max(product, 0)^2.  emit_w / emit_xw / emit_part (epilogue 1, may be null): see the
 // head of this file; emit_part has tuff_gemm_skinny_ctas rows of part_stride >= M floats.
 // scale_part (may be null): [scale_parts, scale_stride] sums of squares of the rows of A's source.
 // Requirements: K % 8 == 0, lda % 8 == 0, ldw % 8 == 0, A and W 16-byte aligned.
@@ -532,7 +539,8 @@ extern "C" int tuff_gemm_skinny(const void* A, const void* W, void* C, int c_dty
                                 const float* scale_part, int scale_parts, int scale_stride, float scale_eps,
                                 int* status, cudaStream_t stream) {
     if (M <= 0 || w_rows <= 0) return 0;
-    if (M > 128 || K <= 0 || epilogue < 0 || epilogue > 2 || !status) return TUFF_E_SIZE;
+    if (M > 128 || K <= 0 || epilogue < 0 || epilogue == 3 || epilogue > 4 || !status) return TUFF_E_SIZE;
+    if (epilogue == EPI_RELU2 && c_dtype != TUFF_BF16) return TUFF_E_DTYPE;
     if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return TUFF_E_ALIGN;
     const bool pair = epilogue == EPI_SWIGLU;
     if (pair && ((w_rows % (2 * BM)) || c_dtype != TUFF_BF16)) return TUFF_E_SIZE;

@@ -53,7 +53,7 @@ constexpr int BK = 64;                       // K elements of one tile: 128 byte
 constexpr int PART_STRIDE = 16;              // floats per CTA in the buffer of partial sums of squares
 constexpr int MAX_TAPS = 4;                  // taps of the convolution whose state is fetched ahead
 
-enum : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_CONV = 3 };
+enum : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_CONV = 3, EPI_RELU2 = 4 };
 
 struct StreamGemm {
     const void* a;            // NORM: fp32 residual [M, K] (lda); else unused (the activations come by TMA)
@@ -460,6 +460,10 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (p.epi == EPI_STORE) {
                 if (p.out_dtype == TUFF_F32) reinterpret_cast<float*>(p.out)[o] = v[0];
                 else store_bf16(v[0]);
+            } else if (p.epi == EPI_RELU2) {
+                // the product rounded to bf16 first, as a separate projection would store it, then max(., 0)^2
+                const float z = fmaxf(bf16_round(v[0]), 0.f);
+                store_bf16(z * z);
             } else if (p.epi == EPI_ACCUM) {
                 float* op = reinterpret_cast<float*>(p.out) + o;
                 const float x_new = (fetched ? pre_res : ld_act(op)) + v[0];
@@ -609,7 +613,7 @@ extern "C" int tuff_gemm_stream_grid(int N) { return N > 0 ? stream_grid(N) : 0;
 
 // epilogue: 0 store, 1 add into fp32 C, 2 swiglu (W is [2N, K]: gate rows then up rows), 3 gated
 // short convolution (W is [3N, K]: B, C, x rows; one token per row of A; taps [N, L], state
-// [slots, L-1, N], slot_of_row [M]).  norm_w: if not null, A is the fp32 residual [M, K] and is
+// [slots, L-1, N], slot_of_row [M]), 4 max(., 0)^2 of the product as bf16.  norm_w: if not null, A is the fp32 residual [M, K] and is
 // RMS-normed with this weight and eps first; else A is bf16 [M, K].
 // Requirements: M <= 8, K % 8 == 0, ldw % 8 == 0, 16-byte aligned bases; bf16 A: lda % 8 == 0;
 // fp32 A: lda % 4 == 0 and K <= 2048.  C is bf16 or fp32 (fp32 only for epilogue 1).
@@ -628,11 +632,11 @@ extern "C" int tuff_gemm_stream(const void* A, const float* norm_w, float eps, c
                                 const float* scale_part, int scale_parts, float scale_eps,
                                 int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 8 || K <= 0 || epilogue < 0 || epilogue > 3 || !status) return TUFF_E_SIZE;
+    if (M > 8 || K <= 0 || epilogue < 0 || epilogue > 4 || !status) return TUFF_E_SIZE;
     if ((K % 8) || (ldw % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return TUFF_E_ALIGN;
     if (norm_w ? (lda % 4 != 0 || ((uintptr_t)norm_w & 15)) : (lda % 8 != 0)) return TUFF_E_ALIGN;
     if (epilogue == EPI_ACCUM && c_dtype != TUFF_F32) return TUFF_E_DTYPE;
-    if ((epilogue == EPI_SWIGLU || epilogue == EPI_CONV) && c_dtype != TUFF_BF16) return TUFF_E_DTYPE;
+    if ((epilogue == EPI_SWIGLU || epilogue == EPI_CONV || epilogue == EPI_RELU2) && c_dtype != TUFF_BF16) return TUFF_E_DTYPE;
     if (c_dtype != TUFF_F32 && c_dtype != TUFF_BF16) return TUFF_E_DTYPE;
     if (epilogue == EPI_CONV && (L < 2 || !taps || !state || !slot_of_row)) return TUFF_E_SIZE;
     if (norm_w && K > NORM_BLOCKS * 1024) return TUFF_E_SIZE;      // a normed row must fit the prologue's registers

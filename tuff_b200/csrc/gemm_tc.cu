@@ -38,7 +38,13 @@ constexpr int BK = 64;             // K elements per stage: 128 bytes of bf16, o
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + tensor memory, warps 2..5: epilogue
 
-enum : int { OUT_STORE = 0, OUT_ACCUM = 1, OUT_PARTIAL = 2, OUT_SWIGLU = 3, OUT_GLU_CLAMP = 4 };
+enum : int { OUT_STORE = 0, OUT_ACCUM = 1, OUT_PARTIAL = 2, OUT_SWIGLU = 3, OUT_GLU_CLAMP = 4, OUT_RELU2 = 5 };
+
+// max(z, 0)^2 of a sum rounded to bf16 first, as a separate projection would store it.
+__device__ __forceinline__ float relu2_of_sum(float acc) {
+    const float z = fmaxf(__bfloat162float(__float2bfloat16_rn(acc)), 0.f);
+    return z * z;
+}
 
 struct GemmParams {
     void* out;            // [rows_of_tokens, ld] bf16 or fp32
@@ -279,6 +285,10 @@ __device__ __forceinline__ void write_tile(const GemmParams& p, uint8_t* stage, 
                 if (c0 >= BN || n0 + c0 >= p.b_rows) break;
                 uint32_t r[16];
                 tmem_ld16(taddr + (uint32_t)c0, r);
+                if (p.mode == OUT_RELU2) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(relu2_of_sum(__uint_as_float(r[j])));
+                }
                 if (rows_ok && n0 + c0 + 16 <= p.b_rows) store16_rows(p, stage, m0 + quad * 32, n0 + c0, lane, r, o[cc]);
                 else if (row < p.a_rows) store16(p, split, row, n0 + c0, r);
             }
@@ -419,7 +429,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
             float* op = (float*)out + idx;
             *op = mode == OUT_ACCUM ? *op + acc : acc;
         } else {
-            ((bf16*)out)[idx] = __float2bfloat16_rn(acc);
+            ((bf16*)out)[idx] = __float2bfloat16_rn(mode == OUT_RELU2 ? relu2_of_sum(acc) : acc);
         }
     }
 }
@@ -454,7 +464,7 @@ extern "C" long long tuff_gemm_tc_workspace_bytes(int m_tokens, int n_out, int k
 // receives a non-zero code if a bounded wait ran out.
 // accumulate == 2: W is [2F, K] laid out as blocks of 128 gate rows followed by their 128 up rows
 // (N = 2F, a multiple of 256), and C [M, F] (bf16, ldc % 8 == 0, 16-byte aligned) receives
-// silu(gate) * up; only for M > 128.
+// silu(gate) * up; only for M > 128.  accumulate == 3: C (bf16) = max(A W^T, 0)^2.
 extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
                             long long lda, long long ldw, long long ldc, int accumulate,
                             float* workspace, long long workspace_bytes, int* status, cudaStream_t stream) {
@@ -466,6 +476,11 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
         if ((ldc % 8) || ((uintptr_t)C & 15)) return TUFF_E_ALIGN;
         accumulate = 0;
     }
+    const bool relu2 = accumulate == 3;
+    if (relu2) {
+        if (c_dtype != TUFF_BF16) return TUFF_E_DTYPE;
+        accumulate = 0;
+    }
     if (accumulate && c_dtype != TUFF_F32) return TUFF_E_DTYPE;
     if ((K % 8) || (lda % 8) || (ldw % 8) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return TUFF_E_ALIGN;
     const int k_blocks = ceil_div(K, BK);
@@ -474,7 +489,7 @@ extern "C" int tuff_gemm_tc(const void* A, const void* W, void* C, int c_dtype, 
     GemmParams p{};
     p.out = C; p.partial = workspace; p.status = status; p.ld = ldc; p.k_blocks = k_blocks;
     p.out_dtype = c_dtype; p.swapped = swapped ? 1 : 0;
-    p.mode = swiglu ? OUT_SWIGLU : accumulate ? OUT_ACCUM : OUT_STORE;
+    p.mode = swiglu ? OUT_SWIGLU : relu2 ? OUT_RELU2 : accumulate ? OUT_ACCUM : OUT_STORE;
     CUtensorMap ma, mb;
     int bn, splits = 1;
     if (swapped) {

@@ -331,9 +331,11 @@ def gemm_tc_eligible(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumu
             and (out.dtype == torch.float32 or not accumulate))
 
 
-def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, swiglu: bool = False) -> None:
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, swiglu: bool = False,
+            relu2: bool = False) -> None:
     """out (=|+=) a @ w.T on the tcgen05 tensor cores (bf16 operands, fp32 accumulation).  `swiglu`:
-    w is a gate/up matrix in blocks of 128 (see stack_gate_up) and out [M, F] = silu(gate) * up."""
+    w is a gate/up matrix in blocks of 128 (see stack_gate_up) and out [M, F] = silu(gate) * up.
+    `relu2`: out (bf16) = max(a @ w.T, 0)^2."""
     _written(out)
     M, K = a.shape
     N = w.shape[0]
@@ -347,7 +349,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: boo
     ws = st["ws"]
     _check(lib.tuff_gemm_tc(_ptr(a), _ptr(w), _ptr(out), dtype_code(out), c_int(M), c_int(N), c_int(K),
                             c_longlong(a.stride(0)), c_longlong(w.stride(0)), c_longlong(out.stride(0)),
-                            c_int(2 if swiglu else 1 if accumulate else 0), _ptr(ws),
+                            c_int(2 if swiglu else 3 if relu2 else 1 if accumulate else 0), _ptr(ws),
                             c_longlong(0 if ws is None else ws.numel() * 4),
                             _ptr(st["status"]), _stream()), "gemm_tc")
 
@@ -428,7 +430,7 @@ class NormedRows:
                 and w.data_ptr() % 16 == 0 and self.x.is_contiguous() and self.x.data_ptr() % 16 == 0)
 
 
-EPI_STORE, EPI_ACCUM, EPI_SWIGLU, EPI_CONV = 0, 1, 2, 3
+EPI_STORE, EPI_ACCUM, EPI_SWIGLU, EPI_CONV, EPI_RELU2 = 0, 1, 2, 3, 4
 
 
 def gemm_decode(a, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE, conv=None, set_block: int = 0) -> None:
@@ -570,7 +572,22 @@ def linear_swiglu(a, w13: torch.Tensor, out: torch.Tensor, block: int = 0) -> No
 
 
 def linear_relu2(a, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out = max(a @ w.T, 0)^2; `a` may be a NormedRows."""
+    """out = max(a @ w.T, 0)^2; `a` may be a NormedRows.  bf16: the activation is the epilogue of the product
+    (the decode product for few tokens, the cluster product up to 128, tcgen05 beyond); the product is rounded to
+    bf16 before it is squared, so that every path gives what the product followed by the activation kernel gives.
+    Everything else (32-bit, sizes that TMA does not take): the product, then the activation kernel."""
+    if out.dtype == torch.bfloat16 and out.stride(1) == 1:
+        if _decode_eligible(a, w, out, False):
+            gemm_decode(a, w, out, EPI_RELU2)
+            return
+        if _cluster_eligible(a, w, out, EPI_RELU2):
+            gemm_cluster(a, w, out, EPI_RELU2)
+            return
+        dense = a.dense() if isinstance(a, NormedRows) else a
+        if gemm_tc_eligible(dense, w, out, False):
+            gemm_tc(dense, w, out, relu2=True)
+            return
+        a = dense
     linear(a, w, out)
     relu2(out)
 
