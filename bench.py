@@ -31,6 +31,9 @@ a 2,048-token prompt in one step and decode steps at batch 1, 8 and 64 (context 
 from device time, and for decode the fraction of the step's HBM bound.
 `--design gimupel` does the same for the Gimupel design (state-space and windowed-attention layers, dense and
 routed feed-forwards) beside Koridra and LFM2 at equal width, depth and active feed-forward width.
+`--design fidinex` does the same for the Fidinex design (several residual streams, attention with learned sinks, attention
+over a latent cache, squared-relu feed-forwards) beside Koridra and LFM2 at equal width, depth and feed-forward parameters.
+`--context N` and `--prefill-only` / `--decode-only`, with --design: another context than 2,048, one half of the points.
 """
 from __future__ import annotations
 
@@ -102,6 +105,27 @@ def gimupel_shape(width, layers, ff, attention_at, experts=16, top=4, vocab=6553
 GIMUPEL_SETS = {
     "1.2b": (gimupel_shape(2048, 16, 5632, (3, 7, 11, 15)), KORIDRA_PAIRS["1.2b"][0], "lfm2.5-1.2b"),
     "350m": (gimupel_shape(1024, 16, 4608, (3, 7, 11, 15)), KORIDRA_PAIRS["350m"][0], "lfm2-350m"),
+}
+
+def fidinex_shape(width, layers, ff, latent_at, streams=4, vocab=65536):
+    """A Fidinex configuration of a real model's proportions: attention layers with heads of 128 in groups of four,
+    normed queries and keys, a learned sink per head, a query temperature with a period of 1,024 positions and values
+    blended with the first layer's; at `latent_at` attention over a latent cache (a latent of 512 and a rotated part of
+    64 per token, heads of 64 + 64 with values of 128); `streams` residual streams; a squared-relu feed-forward of
+    width `ff` (two matrices: 1.5 times a gated one's width gives the same parameters)."""
+    heads = width // 128
+    att = dict(heads=heads, kv_heads=max(1, heads // 4), dim=128, vdim=128, scale=128 ** -0.5, v_mix=True,
+               q_temp=dict(coef=0.1, every=1024))
+    lat = dict(heads=heads, dim=64, rot_dim=64, vdim=128, kv_rank=512, scale=128 ** -0.5, rot=dict(base=10000.0, dims=64))
+    return dict(architecture="Fidinex", vocab=vocab, width=width, norm=dict(eps=1e-5), streams=streams,
+                layers=[dict(type="latent_attention" if i in latent_at else "attention", mixer=lat if i in latent_at else att,
+                             mlp=dict(kind="dense", ff=ff)) for i in range(layers)])
+
+
+# Fidinex beside Koridra and LFM2 at equal width, depth and feed-forward parameters
+FIDINEX_SETS = {
+    "1.2b": (fidinex_shape(2048, 16, 8448, (3, 7, 11, 15)), KORIDRA_PAIRS["1.2b"][0], "lfm2.5-1.2b"),
+    "350m": (fidinex_shape(1024, 16, 6912, (3, 7, 11, 15)), KORIDRA_PAIRS["350m"][0], "lfm2-350m"),
 }
 
 CONTEXT = 8192
@@ -389,7 +413,7 @@ def generic_numbers(cfg_dict):
             for n in need.parts:
                 walk(n)
         elif isinstance(need, PagedKVNeed):
-            kv += need.kv_heads * (need.head_dim + (need.v_head_dim or need.head_dim)) * 2
+            kv += need.kv_heads * (need.head_dim + (0 if need.values_in_keys else (need.v_head_dim or need.head_dim))) * 2
             chunk = need.chunk or need.window or chunk
         elif isinstance(need, StateNeed):
             state += math.prod(need.shape) * 4
@@ -408,12 +432,14 @@ def compare_designs(args) -> int:
     pk, pk_src = peaks()
     rng = np.random.default_rng(0)
     steps, warmup = max(1, min(args.steps, 32)), max(3, args.warmup)
-    context = 2048
+    context = max(64, args.context)
     sampler = ClockSampler()
     sampler.start()
     out = {}
     if args.design == "gimupel":
         sets = {size: (("gimupel", g), ("koridra", k), ("lfm2", SHAPES[l])) for size, (g, k, l) in GIMUPEL_SETS.items()}
+    elif args.design == "fidinex":
+        sets = {size: (("fidinex", f), ("koridra", k), ("lfm2", SHAPES[l])) for size, (f, k, l) in FIDINEX_SETS.items()}
     else:
         sets = {size: (("koridra", k), ("lfm2", SHAPES[l])) for size, (k, l) in KORIDRA_PAIRS.items()}
     only = [x for x in args.models.split(",") if x]
@@ -429,14 +455,15 @@ def compare_designs(args) -> int:
             eng.runner.randomize_cache(1)
             res = {"weight_mb": round(nums["weight_bytes"] / 1e6, 1), "state_kb_per_request": round(nums["state_bytes"] / 1e3, 1),
                    "kv_bytes_per_token": nums["kv_bytes_per_token"]}
-            secs = measure_prefill(eng.runner, cfg, rng, PREFILL_TOKENS, PREFILL_TOKENS)
-            ms = sum(secs) / len(secs) * 1e3
-            # matrices alone: the flops every design of this size has to do on the tensor cores
-            flops = 2.0 * (nums["matmul_params"] - nums["vocab"] * nums["d"]) * PREFILL_TOKENS + 2.0 * nums["vocab"] * nums["d"]
-            res["prefill_2048_tok_s"] = round(PREFILL_TOKENS / ms * 1e3, 1)
-            res["prefill_2048_ms"] = round(ms, 3)
-            res["prefill_matrix_frac"] = round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
-            for b in (1, 8, 64):
+            if not args.decode_only:
+                secs = measure_prefill(eng.runner, cfg, rng, PREFILL_TOKENS, PREFILL_TOKENS)
+                ms = sum(secs) / len(secs) * 1e3
+                # matrices alone: the flops every design of this size has to do on the tensor cores
+                flops = 2.0 * (nums["matmul_params"] - nums["vocab"] * nums["d"]) * PREFILL_TOKENS + 2.0 * nums["vocab"] * nums["d"]
+                res["prefill_2048_tok_s"] = round(PREFILL_TOKENS / ms * 1e3, 1)
+                res["prefill_2048_ms"] = round(ms, 3)
+                res["prefill_matrix_frac"] = round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+            for b in ([] if args.prefill_only else [int(x) for x in args.batches.split(",") if x]):
                 dev_s, _, launches, ctx_mid = measure_decode(eng, b, context, steps, warmup, rng, genuine_prefill=(b == 1))
                 v, pm = mean_pm([b * steps / t for t in dev_s])
                 seen = min(ctx_mid, nums["kv_span"]) if nums["kv_span"] else ctx_mid
@@ -467,9 +494,13 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (recorded)")
     ap.add_argument("--no-points", action="store_true", help="the headline only: no prefill, no other points")
     ap.add_argument("--print-config", choices=sorted(SHAPES), default=None, help="print a shape as a config.json and exit")
-    ap.add_argument("--design", choices=["koridra", "gimupel"], default=None,
-                    help="instead of the default workload: this design beside the LFM2 shape (and, for gimupel, Koridra) of equal size")
+    ap.add_argument("--design", choices=["koridra", "gimupel", "fidinex"], default=None,
+                    help="instead of the default workload: this design beside the LFM2 shape (and, for gimupel and fidinex, Koridra) of equal size")
     ap.add_argument("--models", default="", help="with --design: which of the designs of a set to run, with commas; default all")
+    ap.add_argument("--context", type=int, default=2048, help="with --design: the context of the decode points")
+    ap.add_argument("--prefill-only", action="store_true", help="with --design: the prompt point alone")
+    ap.add_argument("--decode-only", action="store_true", help="with --design: the decode points alone")
+    ap.add_argument("--batches", default="1,8,64", help="with --design: the decode batches, with commas")
     ap.add_argument("--sizes", default="", help="with --design: which of the sizes (1.2b,350m), with commas; default all")
     args = ap.parse_args()
     if args.print_config:

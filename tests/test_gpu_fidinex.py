@@ -22,8 +22,8 @@ pytestmark = pytest.mark.gpu
 # Root mean square of the difference of a logits row (mean taken off) over that of the row itself.
 ROW_TOL = {"float32": 2e-4, "bfloat16": 6e-2}
 LENGTHS = {"fid_a": (70, 45, 97, 130, 66), "fid_b": (83, 40, 129, 65, 100), "fid_c": (150, 64, 37, 200, 129),
-           "fid_d": (120, 51, 33, 160, 101), "fid_e": (300, 129, 517, 64, 200)}
-PAGE = {"fid_a": 16, "fid_b": 4, "fid_c": 64, "fid_d": 8, "fid_e": 32}
+           "fid_d": (120, 51, 33, 160, 101), "fid_e": (300, 129, 517, 64, 200), "fid_f": (190, 64, 131, 260, 77)}
+PAGE = {"fid_a": 16, "fid_b": 4, "fid_c": 64, "fid_d": 8, "fid_e": 32, "fid_f": 16}
 
 
 def row_error(got, ref):
@@ -252,7 +252,8 @@ def test_sink_attention_part_with_blended_values(dtype, H, G, hd, vd, page, q_te
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,dim,rd,vd,rank,page", [(3, 16, 8, 24, 20, 4), (2, 24, 4, 16, 40, 8), (5, 8, 16, 12, 12, 16),
                                                    (4, 32, 32, 32, 64, 64), (2, 40, 64, 20, 200, 8), (16, 64, 32, 64, 128, 32),
-                                                   (1, 16, 0, 16, 32, 4)])
+                                                   (1, 16, 0, 16, 32, 4), (4, 32, 32, 64, 64, 16), (2, 64, 64, 128, 256, 64),
+                                                   (3, 96, 32, 128, 136, 8), (16, 64, 64, 128, 512, 32)])
 def test_latent_attention_part(dtype, H, dim, rd, vd, rank, page):
     from tuff_b200.parts import MIXERS, PartSpec
     rng = np.random.default_rng(H + dim + rank)

@@ -77,7 +77,18 @@ FID_E = dict(
         _att(8, 2, 32, 64, 0.17, None, True, _dense(512)),
     ])
 
-CONFIGS = {"fid_a": (FID_A, 31), "fid_b": (FID_B, 32), "fid_c": (FID_C, 33), "fid_d": (FID_D, 34), "fid_e": (FID_E, 35)}
+# latent layers whose heads are 64 and 128 wide with values as wide: their prompt portions run on expanded keys and
+# values (the tensor-core kernels for prompts), their single tokens in the latent form; two streams
+FID_F = dict(
+    architecture="Fidinex", vocab=640, width=128, norm=dict(eps=1e-5), streams=2,
+    layers=[
+        _lat(4, 32, 32, 64, 64, 0.12, 10000.0, _dense(256)),
+        _att(2, 2, 64, 64, 0.125, (0.2, 32), True, _dense(128)),
+        _lat(2, 64, 64, 128, 256, 0.09, 300.0, _dense(256)),
+        _lat(3, 96, 32, 128, 136, 0.1, 50.0, None),
+    ])
+
+CONFIGS = {"fid_a": (FID_A, 31), "fid_b": (FID_B, 32), "fid_c": (FID_C, 33), "fid_d": (FID_D, 34), "fid_e": (FID_E, 35), "fid_f": (FID_F, 36)}
 
 
 def make_folder(tmp_path, name, with_stream_weights=True):

@@ -720,13 +720,19 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_norm_w: torch.Tensor | None, k_norm_
 
 def latent_prepare(qd: torch.Tensor, ql: torch.Tensor, c_norm_w: torch.Tensor, inv_freq: torch.Tensor,
                    positions: torch.Tensor, row_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
-                   H: int, dim: int, rd: int, rank: int, rot_dims: int, eps: float, write_kv: bool = True) -> None:
+                   H: int, dim: int, rd: int, rank: int, rot_dims: int, eps: float, write_kv: bool = True,
+                   q_in_place: bool = False) -> None:
     """For attention over a latent cache.  qd [n, H*(dim+rd) + rank + rd] is the stacked projection
     [query heads (plain | rotated) | c | kr].  Stores rmsnorm(c) * c_norm_w and the rotated kr as the token's row
     [c | kr] of k_pages [pages, 1, page_size, rank + rd], and the rotated query parts in ql[:, :, rank:]
-    (ql [n, H, rank + rd]; its first `rank` columns per head are left for the absorbed plain parts)."""
+    (ql [n, H, rank + rd]; its first `rank` columns per head are left for the absorbed plain parts).
+    `q_in_place`: the rotated query parts go back into qd instead (ql may be None)."""
     n = qd.shape[0]
-    assert qd.shape[1] == H * (dim + rd) + rank + rd and qd.stride(1) == 1 and ql.shape == (n, H, rank + rd)
+    assert qd.shape[1] == H * (dim + rd) + rank + rd and qd.stride(1) == 1
+    if q_in_place:
+        ql = qd if ql is None else ql
+    else:
+        assert ql.shape == (n, H, rank + rd)
     assert qd.dtype == ql.dtype == k_pages.dtype and k_pages.shape[1] == 1 and k_pages.shape[3] == rank + rd
     assert c_norm_w.dtype == torch.float32 and c_norm_w.numel() == rank
     assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2
@@ -739,7 +745,51 @@ def latent_prepare(qd: torch.Tensor, ql: torch.Tensor, c_norm_w: torch.Tensor, i
                                    c_int(block_table.shape[1]), _ptr(k_pages), c_int(n), c_int(H), c_int(dim), c_int(rd),
                                    c_int(rank), c_int(rot_dims), c_int(k_pages.shape[2]), c_float(eps),
                                    c_int(1 if write_kv else 0), c_longlong(block_table.shape[0]),
-                                   c_longlong(k_pages.shape[0]), _ptr(status_word(qd.device)), _stream()), "latent_prepare")
+                                   c_longlong(k_pages.shape[0]), _ptr(status_word(qd.device)), c_int(1 if q_in_place else 0),
+                                   _stream()), "latent_prepare")
+
+
+def latent_scratch_page() -> int:
+    """Tokens of a scratch page of expanded keys and values."""
+    return int(load_library("latent_attention").tuff_latent_scratch_page())
+
+
+def latent_gather(k_pages: torch.Tensor, block_table: torch.Tensor, meta: torch.Tensor, c_out: torch.Tensor,
+                  rank: int, rd: int) -> None:
+    """The latents (first `rank` elements of the cached rows, bf16) of the tokens of scratch pages into
+    c_out [pages * scratch page, rank].  meta int32 [pages, 4]: the request row (of block_table), the first position
+    and the number of tokens of each scratch page; positions past that number give zeros."""
+    n = meta.shape[0]
+    assert k_pages.dtype == c_out.dtype == torch.bfloat16 and k_pages.shape[1] == 1 and k_pages.shape[3] == rank + rd
+    assert c_out.shape == (n * latent_scratch_page(), rank)
+    _contig(c_out, "c_out"); _contig(k_pages, "k_pages"); _contig(block_table, "block_table"); _contig(meta, "meta")
+    _i32(block_table, "block_table"); _i32(meta, "meta")
+    _written(c_out)
+    lib = load_library("latent_attention")
+    _check(lib.tuff_latent_gather(_ptr(k_pages), _ptr(block_table), c_int(block_table.shape[1]), _ptr(meta), _ptr(c_out),
+                                  c_int(n), c_int(rank), c_int(rd), c_int(k_pages.shape[2]), c_longlong(block_table.shape[0]),
+                                  c_longlong(k_pages.shape[0]), _ptr(status_word(k_pages.device)), _stream()), "latent_gather")
+
+
+def latent_expand_store(kv: torch.Tensor, k_pages: torch.Tensor, block_table: torch.Tensor, meta: torch.Tensor,
+                        k_out: torch.Tensor, v_out: torch.Tensor, H: int, dim: int, rd: int, vd: int, rank: int) -> None:
+    """kv [pages * scratch page, H*dim + H*vd] (bf16): the plain key parts and the values of the scratch tokens, head
+    by head.  Stores k_out [pages, H, scratch page, dim + rd] = [plain part | the token's cached rotated part] and
+    v_out [pages, H, scratch page, vd]."""
+    n = meta.shape[0]
+    sp = latent_scratch_page()
+    assert kv.dtype == k_pages.dtype == k_out.dtype == v_out.dtype == torch.bfloat16
+    assert kv.shape == (n * sp, H * (dim + vd)) and k_out.shape == (n, H, sp, dim + rd) and v_out.shape == (n, H, sp, vd)
+    for t, name in ((kv, "kv"), (k_pages, "k_pages"), (block_table, "block_table"), (meta, "meta"), (k_out, "k_out"), (v_out, "v_out")):
+        _contig(t, name)
+    _i32(block_table, "block_table"); _i32(meta, "meta")
+    _written(k_out); _written(v_out)
+    lib = load_library("latent_attention")
+    _check(lib.tuff_latent_expand_store(_ptr(kv), _ptr(k_pages), _ptr(block_table), c_int(block_table.shape[1]), _ptr(meta),
+                                        _ptr(k_out), _ptr(v_out), c_int(n), c_int(H), c_int(dim), c_int(rd), c_int(vd),
+                                        c_int(rank), c_int(k_pages.shape[2]), c_longlong(block_table.shape[0]),
+                                        c_longlong(k_pages.shape[0]), _ptr(status_word(k_pages.device)), _stream()),
+           "latent_expand_store")
 
 
 def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
@@ -967,6 +1017,9 @@ def _attention_portions(q, k_pages, v_pages, block_table, positions, row_of_toke
         _i32(row_of_token, "row_of_token")
         attention_prefill(q, k_pages, v_pages, block_table, positions, row_of_token, cu_q, out, H, G, hd, scale,
                           window, n_tokens=n_tokens, **opts)
+
+
+attention_portions = _attention_portions
 
 
 # ------------------------------------------------------------ linear attention

@@ -11,6 +11,12 @@ is q~_h . [c | kr]; attention runs over the cached rows with the values being th
 elements, and V_h is applied to the weighted sum of latents afterwards.  This is the same sum in another
 order; scores, softmax, the norm of c and the rotation are fp32.
 
+Portions of prompts (bf16, heads of 64 or 128 with values as wide) take the other order: a portion has as many
+queries as keys, so the cached rows of its request are expanded once into keys [U_h c | kr] and values V_h c per
+head, in scratch pages shared by all layers, and the tensor-core attention kernels for prompts run over those
+(a quarter of the multiplications of the latent form, at the sizes usual for this mixer).  Rows that bring a single
+token stay in the latent form; a batch that mixes both runs each kind its own way.
+
 Weights: `q` [H (dim + rot_dim), d], `dkv` [kv_rank + rot_dim, d], `dkv_norm` [kv_rank], `uk` [H dim, kv_rank],
 `uv` [H vdim, kv_rank], `sink` [H], `o` [d, H vdim].  The rotation pairs neighbouring elements (2i, 2i+1) of the
 first `rot_dims` elements of the rotated part, at the angle pos * rot_base^(-2i / rot_dims).
@@ -41,6 +47,7 @@ class LatentAttention(Mixer):
             raise ValueError(f"latent_attention: sink {sink!r}; choose learned or None")
         self.learned_sink = sink == "learned"
         self._inv_freq = None
+        self._cap_pages = 0
 
     def weight_decls(self):
         H, d = self.H, self.d
@@ -69,22 +76,116 @@ class LatentAttention(Mixer):
         inv = (self.rot_base ** (-2.0 * i / max(self.rot_dims, 1))).astype(np.float32)
         self._inv_freq = torch.from_numpy(inv).to(self.wo.device)
         self.w = {"o": self.wo}
+        # prompt portions by expansion: the products' matrix [U; V], and whether the sizes suit the tensor-core kernels
+        hq = self.dim + self.rd
+        self.expands = (act_dtype == torch.bfloat16 and hq == self.vd and hq in (64, 128)
+                        and self.dim % 8 == 0 and self.rd % 8 == 0 and self.rank % 8 == 0)
+        self.w_exp = torch.cat([weights["uk"], weights["uv"]], dim=0).contiguous() if self.expands else None
+
+    # ---- scratch pages of expanded keys and values: one buffer per device, shared by all layers ---------------------
+    _scratch: dict = {}
+
+    def _per_page(self):
+        """bf16 elements of scratch a page of expanded tokens needs: latents, the products' output, keys, values."""
+        H, hq = self.H, self.dim + self.rd
+        return ops.latent_scratch_page() * (self.rank + H * (self.dim + self.vd) + H * hq + H * self.vd)
+
+    def _buffers(self, device, pages):
+        need = pages * self._per_page()
+        buf = LatentAttention._scratch.get(device)
+        if buf is None or buf.numel() < need:
+            buf = LatentAttention._scratch[device] = torch.empty(need, dtype=torch.bfloat16, device=device)
+        SP, H, hq, vd = ops.latent_scratch_page(), self.H, self.dim + self.rd, self.vd
+        o, out = 0, []
+        for shape in ((pages * SP, self.rank), (pages * SP, H * (self.dim + vd)), (pages, H, SP, hq), (pages, H, SP, vd)):
+            n = int(np.prod(shape))
+            out.append(buf[o:o + n].view(shape))
+            o += n
+        return out
+
+    def reserve(self, device, max_rows, max_context):
+        if self.expands:
+            device = torch.device(device)
+            self._cap_pages = -(-max(int(max_context), 8192) // ops.latent_scratch_page()) + 4
+            self._buffers(device, self._cap_pages)
+
+    @staticmethod
+    def _plan(ctx, cap_pages):
+        """Groups of prompt rows (those after the leading one-token rows) whose contexts fit the scratch pages together;
+        per group the scratch pages' sources and the rows' tables of scratch pages.  Made once per step, on the host."""
+        key = ("latent_expand", cap_pages)
+        plan = ctx.extra.get(key)
+        if plan is not None:
+            return plan
+        SP = ops.latent_scratch_page()
+        cu, pos = ctx.host["cu_q"], ctx.host["positions"]
+        groups, cur = [], None
+        for r in range(ctx.single_prefix, ctx.n_rows):
+            n_ctx = int(pos[cu[r + 1] - 1]) + 1
+            pages = -(-n_ctx // SP)
+            if cur is None or cur["pages"] + pages > cap_pages:
+                cur = dict(rows=[], pages=0)
+                groups.append(cur)
+            cur["rows"].append((r, n_ctx, cur["pages"], pages))
+            cur["pages"] += pages
+        parts = []
+        for g in groups:
+            width = max(p for _, _, _, p in g["rows"])
+            meta = np.zeros((g["pages"], 4), np.int32)
+            table = np.full((len(g["rows"]), width), -1, np.int32)
+            for i, (r, n_ctx, first, pages) in enumerate(g["rows"]):
+                for b in range(pages):
+                    meta[first + b] = (r, b * SP, min(SP, n_ctx - b * SP), 0)
+                table[i, :pages] = np.arange(first, first + pages)
+            g["meta_at"], g["table_at"], g["width"] = len(parts), len(parts) + 1, width
+            parts += [meta.reshape(-1), table.reshape(-1)]
+        flat = np.concatenate([np.pad(p, (0, -p.size % 4)) for p in parts]) if parts else np.zeros(4, np.int32)
+        dev = torch.from_numpy(flat).to(ctx.device, non_blocking=False)
+        offs = np.cumsum([0] + [p.size + (-p.size % 4) for p in parts])
+        for g in groups:
+            a, b = offs[g["meta_at"]], offs[g["table_at"]]
+            g["meta"] = dev[a:a + g["pages"] * 4].view(g["pages"], 4)
+            g["table"] = dev[b:b + len(g["rows"]) * g["width"]].view(len(g["rows"]), g["width"])
+        ctx.extra[key] = groups
+        return groups
 
     def forward(self, ctx, cache, h, residual, reads_only=False):
         T = h.shape[0]
         H, dim, rd, rank, vd = self.H, self.dim, self.rd, self.rank, self.vd
-        hl = rank + rd
+        hl, hq = rank + rd, dim + rd
         dev = h.device
-        qd = torch.empty((T, H * (dim + rd) + hl), dtype=self.act_dtype, device=dev)
+        qd = torch.empty((T, H * hq + hl), dtype=self.act_dtype, device=dev)
         ops.linear(h, self.w_in, qd)
-        ql = torch.empty((T, H, hl), dtype=self.act_dtype, device=dev)          # the query in the latent space
         table = ctx.block_tables[cache.group]
-        ops.latent_prepare(qd, ql, self.c_norm, self._inv_freq, ctx.positions, ctx.row_of_token, table, cache.k_pages,
-                           H, dim, rd, rank, self.rot_dims, self.eps, write_kv=not reads_only)
-        ops.head_linear(qd[:, : H * (dim + rd)].unflatten(1, (H, dim + rd))[:, :, :dim], self.ukt, ql[:, :, :rank])
-        lat = torch.empty((T, H * rank), dtype=self.act_dtype, device=dev)
-        ops.paged_attention(ql.view(T, H * hl), cache.k_pages, None, table, ctx.positions, ctx.row_of_token, lat,
-                            H, 1, hl, self.scale, 0, ctx=ctx, sink=self.sinks, v_head_dim=rank, values_in_keys=True)
         att = torch.empty((T, H, vd), dtype=self.act_dtype, device=dev)
-        ops.head_linear(lat.view(T, H, rank), self.uv, att)
+        # tokens [0, n1) belong to the leading rows of one token: the latent form; the rest are prompt portions
+        expand = self.expands and not ctx.all_single and "cu_q" in ctx.host and "positions" in ctx.host
+        n1 = (int(ctx.host["cu_q"][ctx.single_prefix]) if expand else T)
+        if n1 > 0:
+            ql = torch.empty((T, H, hl), dtype=self.act_dtype, device=dev)          # the query in the latent space
+            ops.latent_prepare(qd, ql, self.c_norm, self._inv_freq, ctx.positions, ctx.row_of_token, table, cache.k_pages,
+                               H, dim, rd, rank, self.rot_dims, self.eps, write_kv=not reads_only)
+            ops.head_linear(qd[:n1, : H * hq].unflatten(1, (H, hq))[:, :, :dim], self.ukt, ql[:n1, :, :rank])
+            lat = torch.empty((n1, H * rank), dtype=self.act_dtype, device=dev)
+            ops.paged_attention(ql[:n1].view(n1, H * hl), cache.k_pages, None, table[:ctx.single_prefix] if expand else table,
+                                ctx.positions[:n1], ctx.row_of_token[:n1], lat, H, 1, hl, self.scale, 0,
+                                cu_q=None if expand else ctx.cu_q, all_single=True if expand else ctx.all_single,
+                                max_seq_len=ctx.max_seq_len, single_prefix=0 if expand else ctx.single_prefix,
+                                sink=self.sinks, v_head_dim=rank, values_in_keys=True)
+            ops.head_linear(lat.view(n1, H, rank), self.uv, att[:n1])
+        if n1 < T:
+            # the portions: rotated queries in place (the cache rows are written by the first call, if there was one)
+            ops.latent_prepare(qd, None, self.c_norm, self._inv_freq, ctx.positions, ctx.row_of_token, table, cache.k_pages,
+                               H, dim, rd, rank, self.rot_dims, self.eps, write_kv=(n1 == 0 and not reads_only),
+                               q_in_place=True)
+            cap = max(self._cap_pages, -(-int(ctx.max_seq_len) // ops.latent_scratch_page()))
+            for g in self._plan(ctx, cap):
+                c_all, kv, ks, vs = self._buffers(dev, g["pages"])
+                ops.latent_gather(cache.k_pages, table, g["meta"], c_all, rank, rd)
+                ops.linear(c_all, self.w_exp, kv)
+                ops.latent_expand_store(kv, cache.k_pages, table, g["meta"], ks, vs, H, dim, rd, vd, rank)
+                a, b = g["rows"][0][0], g["rows"][-1][0] + 1
+                n_tok = int(ctx.host["cu_q"][b] - ctx.host["cu_q"][a])
+                ops.attention_portions(qd, ks, vs, g["table"], ctx.positions, ctx.row_of_token, ctx.cu_q[a:b + 1],
+                                       att.view(T, H * vd), H, H, hq, self.scale, 0, n_tokens=n_tok, sink=self.sinks)
         ops.linear(att.view(T, H * vd), self.wo, residual, accumulate=True)
