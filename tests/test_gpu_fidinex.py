@@ -420,6 +420,74 @@ def test_one_far_key_among_hundreds_and_learned_sinks(dtype, kd, vd, page, in_ke
     assert abs(share[0, 0] - 0.5) < 1e-12
 
 
+@pytest.mark.parametrize("H,rank,rd,page,splits", [(4, 64, 32, 16, 0), (16, 128, 64, 64, 3), (20, 72, 8, 8, 5), (33, 512, 64, 32, 0),
+                                                   (1, 32, 0, 4, 32), (7, 200, 24, 16, 2)])
+def test_latent_decode_kernel_far_keys_and_sinks(monkeypatch, H, rank, rd, page, splits):
+    """Single tokens of two requests over a latent cache, every head in one pass: one cached row whose score stands
+    out for two heads (at the first place, at a page's edges, at a tile's edges, far back), a sink that takes a head's
+    whole weight and sinks that take a share; contexts of 1 to 400 rows, with the keys cut into 1 to 32 slices
+    (more slices than tiles too).  Against the sums written out in float64."""
+    from tuff_b200.kernels import ops
+    if splits:
+        monkeypatch.setenv("TUFF_LATENT_SPLITS", str(splits))
+    hl, T = rank + rd, 400
+    rng = np.random.default_rng(H * rank + page)
+    bf = torch.bfloat16
+    assert ops.latent_decode_supported(torch.empty(1, dtype=bf), torch.empty(1, dtype=bf), H, rank, rd)
+    sinks = rng.normal(size=H); sinks[0] = 40.0; sinks[-1] = -30.0
+    hot = [h for h in (1, H - 1) if h < H and h > 0] or [0]
+    for key_at in (0, page - 1, page, 63, 64, 137):
+        rows = f64(dev(0.1 * rng.normal(size=(2, T, hl)), bf))
+        rows[0, key_at] = 0.0; rows[0, key_at, hl - 1] = 6.0; rows[0, key_at, :rank] = np.arange(rank) % 5 - 2.0
+        if rd == 0:                                   # no rotated part: the score's column lies inside the values
+            rows[0, key_at, :rank] = 0.0; rows[0, key_at, rank - 1] = 6.0
+        n_pages = -(-T // page)
+        kp = torch.zeros(2 * n_pages + 1, 1, page, hl, device="cuda", dtype=bf)
+        table = torch.arange(2 * n_pages, dtype=torch.int32, device="cuda").flip(0).reshape(2, n_pages).contiguous()
+        for r in range(2):
+            full = torch.zeros(n_pages * page, hl, device="cuda", dtype=bf)
+            full[:T] = dev(rows[r], bf)
+            kp[table[r].long(), 0] = full.view(n_pages, page, hl)
+        places = sorted({0, 1, key_at, max(0, key_at - 1), key_at + 1, 62, 63, 64, 65, 127, 128, 200, 399})
+        pos = np.array([q for q in places for _ in range(2)]); row_of = np.array([0, 1] * len(places))
+        n = len(pos)
+        ql = f64(dev(0.1 * rng.normal(size=(n, H, hl)), bf))
+        for h in hot:
+            ql[:, h, hl - 1] = 5.0
+        out = torch.full((n, H, rank), 7.0, device="cuda", dtype=bf)
+        ops.latent_decode(dev(ql, bf), kp, table, dev(pos, torch.int32), dev(row_of, torch.int32), out, H, rank, rd, 0.9,
+                          sink=dev(sinks), max_seq_len=T)
+        got = f64(out)
+        for i in range(n):
+            keys = rows[row_of[i], : pos[i] + 1]
+            for h in range(H):
+                sc = 0.9 * keys @ ql[i, h]
+                wts = plain.sink_softmax(sc[None, :], sinks[h], np.ones((1, len(sc)), bool))[0]
+                ref = wts @ keys[:, :rank]
+                assert np.abs(got[i, h] - ref).max() <= 2e-2 * max(1.0, np.abs(ref).max()), (key_at, i, h)
+        if H > 1:
+            assert np.abs(got[:, 0]).max() < 1e-6                               # the sink of head 0 keeps everything
+        seen = [i for i in range(n) if row_of[i] == 0 and pos[i] >= key_at]
+        if rd and H > 1 and sinks[hot[-1]] < 10:
+            for i in seen:                                                       # the far row alone, whole, for the heads that ask
+                assert np.abs(got[i, hot[-1]] - rows[0, key_at, :rank]).max() < 0.1
+
+
+@pytest.mark.parametrize("T,H,K,N", [(1, 3, 16, 20), (8, 16, 64, 128), (9, 5, 130, 7), (64, 2, 512, 64), (128, 1, 24, 33)])
+def test_head_linear_of_few_rows(T, H, K, N):
+    """A matrix per head applied to views with strides (heads inside wider rows), few tokens: the one-warp-per-column kernel."""
+    from tuff_b200.kernels import ops
+    rng = np.random.default_rng(T + K)
+    bf = torch.bfloat16
+    wide = dev(rng.normal(size=(T, H, K + 6)), bf)
+    w = dev(rng.normal(size=(H, N, K)) / math.sqrt(K), bf)
+    outw = torch.zeros(T, H, N + 2, device="cuda", dtype=bf)
+    ops.head_linear(wide[:, :, 2:2 + K], w, outw[:, :, :N])
+    ref = np.einsum("thk,hnk->thn", f64(wide[:, :, 2:2 + K]), f64(w))
+    assert np.abs(f64(outw[:, :, :N]) - ref).max() <= 1e-2 * max(1.0, np.abs(ref).max())
+    assert float(outw[:, :, N:].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("hd,vd,page", [(16, 16, 4), (64, 64, 16), (128, 128, 32), (24, 40, 8)])
 def test_learned_sinks_take_their_share(hd, vd, page):
     """Scores of zero over n keys and sinks ln(1), ln(3), -inf-like: the weights are 1 / (n + e^sink)."""

@@ -252,10 +252,12 @@ def test_attention_finds_a_far_key_and_respects_the_window(dtype, hd, blocked):
 
 @pytest.mark.parametrize("H,G,page,window", [(4, 2, 16, 0), (3, 1, 64, 0), (12, 2, 8, 100), (2, 2, 64, 129), (9, 3, 32, 0)])
 def test_attention_prefill_tc_long_portions(H, G, page, window):
-    """The tcgen05 kernel for prompt portions (head size 64): requests whose portions span several
+    """The tcgen05 kernel for prompt portions (head sizes 64 and 128): requests whose portions span several
     128-token blocks and many 64-key tiles, start inside a page and inside a tile, with and without
     a window, beside a single-token request; never-written cache slots hold NaN.  Against fp64."""
     portions_case(H, G, page, window, (0, 70, 513, 5, 200), (300, 200, 129, 1, 128), 0)
+    # head size 128: two column blocks of 64
+    portions_case(H, G, page, window, (0, 70, 513, 5, 200), (300, 200, 129, 1, 128), 0, hd=128)
 
 
 @pytest.mark.parametrize("H,G,page,window", [(4, 2, 16, 0), (12, 2, 8, 100), (8, 8, 64, 0)])
@@ -264,7 +266,7 @@ def test_attention_of_decoding_rows_beside_portions(H, G, page, window):
     the decoding rows go to the sliced kernel and the portions to the blocked one, each with its
     own part of the tables.  Against fp64."""
     portions_case(H, G, page, window, (300, 70, 513, 5, 200, 64), (1, 1, 1, 140, 128, 2), 3)
-    # head size 128: the sliced kernel beside the blocked mma.sync kernel
+    # head size 128: the sliced kernel beside the blocked one
     portions_case(H, G, page, window, (300, 70, 513, 5, 200, 64), (1, 1, 1, 140, 128, 2), 3, hd=128)
 
 
@@ -289,7 +291,7 @@ def portions_case(H, G, page, window, starts, lens, single_prefix, hd=64):
     pos = np.concatenate([np.arange(a, a + n) for a, n in zip(starts, lens)])
     row_of = np.repeat(np.arange(len(lens)), lens)
     cu = np.concatenate([[0], np.cumsum(lens)])
-    assert ops.attention_prefill_tc_supported(q, kp, H, G, hd) == (hd == 64)
+    assert ops.attention_prefill_tc_supported(q, kp, H, G, hd) == (hd in (64, 128))
     out = torch.full((sum(lens), H * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
     ops.paged_attention(q, kp, vp, dev(table, torch.int32), dev(pos, torch.int32), dev(row_of, torch.int32), out, H, G, hd,
                         1 / math.sqrt(hd), window=window, cu_q=dev(cu, torch.int32), all_single=False, max_seq_len=max(seqs),

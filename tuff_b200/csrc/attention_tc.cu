@@ -1,5 +1,5 @@
 // Causal attention of prompt portions over the paged cache on the Blackwell tensor cores
-// (tcgen05.mma, accumulators in tensor memory), head size 64.
+// (tcgen05.mma, accumulators in tensor memory), head sizes 64 and 128.
 //
 // One CTA takes 128 consecutive query tokens of one request and one query head and walks the
 // 64-key tiles its tokens can see.  Per tile:
@@ -23,6 +23,10 @@
 // thread issues S of tile j+1 before P V of tile j, so the tensor cores work on the next scores
 // while the softmax warps are busy with the current ones.  Two CTAs fit on an SM (256 of the 512
 // TMEM columns each: S twice 64, O 64, P twice 32).
+// A head of 128 is two column blocks of 64 dims: Q, K and V tiles lie in shared memory block after
+// block (each [rows][64 dims], rows of 128 bytes, the layout a 128-byte-swizzle box of TMA writes),
+// S sums the products of both blocks, and P V is issued once per block of V into its half of O.
+// That CTA holds 320 columns (all 512 are allocated) and 160 KB of shared memory: one per SM.
 //
 // Online softmax as in the reference's kernel (src/lfm25_gpu.cu:506-558: scale 1/sqrt(hd) :520,
 // head-to-group map :518, causal bound :531), which handles one key at a time per block.
@@ -80,8 +84,8 @@ template <int HD> __host__ __device__ constexpr uint32_t idesc_pv() {          /
     return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(QROWS >> 4) << 24);
 }
 template <int HD> struct Smem {
-    static constexpr int Q = 0;                               // [128][64] bf16
-    static constexpr int KV = Q + QROWS * 128;                // STAGES x (K tile, V tile)
+    static constexpr int Q = 0;                               // HD / 64 blocks of [128][64] bf16
+    static constexpr int KV = Q + QROWS * HD * 2;             // STAGES x (K tile, V tile), each HD / 64 blocks of [64][64]
     static constexpr int STAGE_BYTES = 2 * TILE * HD * 2;
     static constexpr int BARS = KV + STAGES * STAGE_BYTES;
     static constexpr int N_BARS = 1 + 2 * STAGES + 8;
@@ -97,9 +101,11 @@ __device__ __forceinline__ void store_row_swizzled(uint8_t* tile, int row, const
 }
 
 template <int HD>
-__global__ void __launch_bounds__(NUM_THREADS, 2)
+__global__ void __launch_bounds__(NUM_THREADS, HD == 64 ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_constant__ CUtensorMap mv, TcAttnParams p) {
-    static_assert(HD == 64, "head size 64 only");
+    static_assert(HD == 64 || HD == 128, "head sizes 64 and 128");
+    constexpr int CB = HD / 64;                      // column blocks of 64 dims
+    constexpr int BLK_Q = QROWS * 128, BLK_KV = TILE * 128;      // bytes of one block of Q, of K or V
     using L = Smem<HD>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -145,7 +151,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    constexpr uint32_t TMEM_COLS = 256;                        // S twice (128), O (64), P twice (32 each)
+    constexpr uint32_t TMEM_COLS = HD == 64 ? 256 : 512;      // S twice (128), O (HD), P twice (32 each); a power of two
     if (warp == 5) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(base + (uint32_t)L::TMEM_SLOT), "r"(TMEM_COLS) : "memory");
@@ -178,8 +184,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
                     }
                     const int y = (page * p.G + g) * p.page_size;                   // a missing page lies outside the tensor: zero fill
                     const uint32_t off = (uint32_t)(i * p.page_size) * 128;
-                    tma_load_2d(sK + off, &mk, kv_full(s), 0, y);
-                    tma_load_2d(sV + off, &mv, kv_full(s), 0, y);
+#pragma unroll
+                    for (int cb = 0; cb < CB; ++cb) {                               // x = 0 or 64 elements: 128-byte steps
+                        tma_load_2d(sK + cb * BLK_KV + off, &mk, kv_full(s), 64 * cb, y);
+                        tma_load_2d(sV + cb * BLK_KV + off, &mv, kv_full(s), 64 * cb, y);
+                    }
                 }
             }
         }
@@ -196,8 +205,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
                     tc_fence_after();
                     const uint32_t sK = base + L::KV + s * L::STAGE_BYTES;
 #pragma unroll
-                    for (int k = 0; k < HD / 16; ++k)
-                        umma(tmem_s + b * TILE, smem_desc_k_major(sQ + k * 32), smem_desc_k_major(sK + k * 32), IDESC_S, k > 0 ? 1u : 0u);
+                    for (int cb = 0; cb < CB; ++cb)
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            umma(tmem_s + b * TILE, smem_desc_k_major(sQ + cb * BLK_Q + k * 32), smem_desc_k_major(sK + cb * BLK_KV + k * 32),
+                                 IDESC_S, (cb > 0 || k > 0) ? 1u : 0u);
                     umma_commit(s_full(b));
                 }
                 if (j > 0) {
@@ -206,8 +218,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
                     tc_fence_after();
                     const uint32_t sV = base + L::KV + s * L::STAGE_BYTES + TILE * HD * 2;
 #pragma unroll
-                    for (int k = 0; k < TILE / 16; ++k)
-                        umma_ts(tmem_o, tmem_p + b * (TILE / 2) + k * 8, desc_mn_major(sV + k * 2048), idesc_pv<HD>(), (jj > 0 || k > 0) ? 1u : 0u);
+                    for (int cb = 0; cb < CB; ++cb)
+#pragma unroll
+                        for (int k = 0; k < TILE / 16; ++k)
+                            umma_ts(tmem_o + 64 * cb, tmem_p + b * (TILE / 2) + k * 8, desc_mn_major(sV + cb * BLK_KV + k * 2048),
+                                    idesc_pv<64>(), (jj > 0 || k > 0) ? 1u : 0u);
                     umma_commit(pv_full(b));
                     umma_commit(kv_empty(s));          // K and V of the stage have been read once these retire
                 }
@@ -225,14 +240,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
         const bool warp_valid = warp * 32 < n_here;
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         {   // this row of Q into shared memory (zeros beyond the portion)
-            uint32_t w[32];
             const bf16* qrow = p.q + (size_t)(q0 + (valid ? r : 0)) * p.q_stride + (size_t)h * HD;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint4 v = valid ? ld_act_u4(qrow + 8 * c) : make_uint4(0u, 0u, 0u, 0u);
-                w[4 * c] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
+            for (int cb = 0; cb < CB; ++cb) {
+                uint32_t w[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    uint4 v = valid ? ld_act_u4(qrow + 64 * cb + 8 * c) : make_uint4(0u, 0u, 0u, 0u);
+                    w[4 * c] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
+                }
+                store_row_swizzled(base_ptr + L::Q + cb * BLK_Q, r, w);
             }
-            store_row_swizzled(base_ptr + L::Q, r, w);
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(q_ready);
@@ -254,8 +272,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
                 if (!mbar_wait(kv_full(s), (j / STAGES) & 1, p.status, 38)) { ok = false; break; }
                 uint8_t* sV = base_ptr + L::KV + s * L::STAGE_BYTES + TILE * HD * 2;
                 const int first = pos_last + 1 - key0;                              // 1..63
-                for (int i = first * 8 + r; i < TILE * 8; i += QROWS)
-                    *reinterpret_cast<uint4*>(sV + i * 16) = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for (int cb = 0; cb < CB; ++cb)
+                    for (int i = first * 8 + r; i < TILE * 8; i += QROWS)
+                        *reinterpret_cast<uint4*>(sV + cb * BLK_KV + i * 16) = make_uint4(0u, 0u, 0u, 0u);
                 fence_async_smem();                                                 // before the MMA reads them
             }
             float mx = -INFINITY;
@@ -358,7 +378,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mk, const __grid_cons
 
 // ------------------------------------------------------------------ host side
 bool supported(int H, int G, int hd, int page_size) {
-    if (hd != 64) return false;
+    if (hd != 64 && hd != 128) return false;
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64) return false;
     return G >= 1 && H % G == 0;
 }
@@ -390,13 +410,16 @@ extern "C" int tuff_attention_prefill_tc(const void* q, long long q_stride, cons
     p.chunk = chunk; p.has_sink = (has_sink || sinks) ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.sinks = sinks; p.out_scale = out_scale;
     p.n_blocks = (n_tokens + QROWS - 1) / QROWS + n_rows;      // an upper bound on the blocks of all requests
     p.scale_log2 = scale * 1.4426950408889634f;
-    const int smem = Smem<64>::TOTAL;
     static bool set = false;
     if (!set) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::TOTAL);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attn_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL);
         if (e != cudaSuccess) return (int)e;
         set = true;
     }
-    const int rc = launch_pdl(attn_prefill_tc_kernel<64>, dim3((unsigned)(p.n_blocks * H)), dim3(NUM_THREADS), smem, stream, mk, mv, p);
+    const dim3 grid((unsigned)(p.n_blocks * H));
+    const int rc = hd == 64 ? launch_pdl(attn_prefill_tc_kernel<64>, grid, dim3(NUM_THREADS), Smem<64>::TOTAL, stream, mk, mv, p)
+                            : launch_pdl(attn_prefill_tc_kernel<128>, grid, dim3(NUM_THREADS), Smem<128>::TOTAL, stream, mk, mv, p);
     return rc ? rc : launch_status();
 }

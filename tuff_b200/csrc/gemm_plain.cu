@@ -74,6 +74,44 @@ gemm_plain_kernel(const AT* __restrict__ A, const WT* __restrict__ W, CT* __rest
         }
     }
 }
+// A batch of products with few rows (bf16): C[m, n] = sum_k A[m, k] W[n, k] for up to HR_ROWS rows m per CTA.
+// One warp per output column n: its lanes take pairs of k in turn, every lane keeps one sum per row, and the
+// lanes' sums are added by shuffles, so an element's value depends on K alone.  The weights are read once
+// per HR_ROWS rows, in whole lines.
+constexpr int HR_ROWS = 8, HR_WARPS = 8;
+__global__ void __launch_bounds__(HR_WARPS * 32)
+head_rows_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, bf16* __restrict__ C, int M, int N, int K,
+                 long long lda, long long ldw, long long ldc, long long sa, long long sw, long long sc) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * HR_WARPS + warp, m0 = blockIdx.z * HR_ROWS;
+    A += (size_t)blockIdx.y * sa + (size_t)m0 * lda; W += (size_t)blockIdx.y * sw; C += (size_t)blockIdx.y * sc + (size_t)m0 * ldc;
+    pdl_wait();
+    pdl_launch_dependents();
+    if (n >= N) return;
+    const int rows = min(HR_ROWS, M - m0);
+    float acc[HR_ROWS];
+#pragma unroll
+    for (int i = 0; i < HR_ROWS; ++i) acc[i] = 0.f;
+    const bf16* wrow = W + (size_t)n * ldw;
+    for (int k = 2 * lane; k < K; k += 64) {
+        const float2 w = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(wrow + k));
+#pragma unroll
+        for (int i = 0; i < HR_ROWS; ++i) {
+            if (i < rows) {
+                const uint32_t raw = ld_act_u32(A + (size_t)i * lda + k);
+                const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw));
+                acc[i] = fmaf(a.y, w.y, fmaf(a.x, w.x, acc[i]));
+            }
+        }
+    }
+    float mine = 0.f;
+#pragma unroll
+    for (int i = 0; i < HR_ROWS; ++i) {
+        const float v = warp_sum(acc[i]);
+        if (lane == i) mine = v;
+    }
+    if (lane < rows) C[(size_t)lane * ldc + n] = __float2bfloat16_rn(mine);
+}
 }  // namespace
 
 // `batch` products in one launch: product b reads A + b*sa, W + b*sw and writes C + b*sc (strides in elements).
@@ -108,4 +146,16 @@ extern "C" int tuff_gemm_plain(const void* A, int a_dtype, const void* W, int w_
                                int M, int N, int K, long long lda, long long ldw, long long ldc,
                                int accumulate, cudaStream_t stream) {
     return tuff_gemm_plain_batched(A, a_dtype, W, w_dtype, C, c_dtype, M, N, K, lda, ldw, ldc, 1, 0, 0, 0, accumulate, stream);
+}
+
+// The same batch for few rows (M small against N), bf16 throughout: one warp per output column.  K and all
+// strides even, the pointers 4-byte aligned; else TUFF_E_ALIGN and the caller takes the general kernel.
+extern "C" int tuff_head_rows(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw,
+                              long long ldc, int batch, long long sa, long long sw, long long sc, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    if (K <= 0 || batch > 65535 || ceil_div(M, HR_ROWS) > 65535) return TUFF_E_SIZE;
+    if ((K | lda | ldw | sa | sw) & 1) return TUFF_E_ALIGN;
+    if (((uintptr_t)A | (uintptr_t)W) & 3) return TUFF_E_ALIGN;
+    return launch_pdl(head_rows_kernel, dim3(ceil_div(N, HR_WARPS), batch, ceil_div(M, HR_ROWS)), dim3(HR_WARPS * 32), 0, stream,
+                      (const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, ldw, ldc, sa, sw, sc);
 }

@@ -9,8 +9,8 @@
 //                  y is cleared after it was read, so the sublayer that follows can add into it again.
 //   tuff_relu2     z <- max(z, 0)^2 in place, the activation of a feed-forward without a gate.
 //
-// Everything is fp32 but h.  One block per token; a thread's columns and the order of every sum depend
-// on the width alone, so a token's result does not depend on the batch it is in.
+// Everything is fp32 but h.  One block per token; a thread's columns (four neighbours at a time where the width
+// is a multiple of four) and the order of every sum depend on the width and the alignment alone, so a token's result does not depend on the batch it is in.
 #include "common.cuh"
 
 namespace {
@@ -32,10 +32,23 @@ struct HcParams {
     int zero_y;
 };
 
-template <typename TH, int S>
+// V consecutive columns (1, or 4 where the width and the pointers allow: one 16-byte access each).
+template <int V> struct HcVec { float v[V]; };
+template <int V> __device__ __forceinline__ HcVec<V> hc_load(const float* p) {
+    HcVec<V> r;
+    if constexpr (V == 4) { const float4 q = __ldcg(reinterpret_cast<const float4*>(p)); r.v[0] = q.x; r.v[1] = q.y; r.v[2] = q.z; r.v[3] = q.w; }
+    else r.v[0] = ld_act(p);
+    return r;
+}
+template <int V> __device__ __forceinline__ void hc_store(float* p, const HcVec<V>& r) {
+    if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+    else *p = r.v[0];
+}
+
+template <typename TH, int S, int V>
 __global__ void __launch_bounds__(HC_THREADS)
 hc_step_kernel(HcParams p) {
-    extern __shared__ float u_row[];           // [d]
+    extern __shared__ __align__(16) float u_row[];           // [d]
     __shared__ float scratch[32];
     __shared__ float sh_mix[HC_MAX_S * HC_MAX_S], sh_out[HC_MAX_S], sh_in[HC_MAX_S];
     const int t = blockIdx.x;
@@ -50,45 +63,56 @@ hc_step_kernel(HcParams p) {
     __syncthreads();
     const size_t row = (size_t)t * p.d, plane = (size_t)p.T * p.d;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < p.d; c += HC_THREADS) {
-        float nx[S];
+    for (int c = threadIdx.x * V; c < p.d; c += HC_THREADS * V) {
+        HcVec<V> nx[S];
         if (p.x_init) {
-            const float v = ld_act(p.x_init + row + c);
+            const HcVec<V> v = hc_load<V>(p.x_init + row + c);
 #pragma unroll
-            for (int s = 0; s < S; ++s) { nx[s] = v; p.X[s * plane + row + c] = v; }
+            for (int s = 0; s < S; ++s) { nx[s] = v; hc_store<V>(p.X + s * plane + row + c, v); }
         } else {
-            float x[S];
+            HcVec<V> x[S];
 #pragma unroll
-            for (int s = 0; s < S; ++s) x[s] = ld_act(p.X + s * plane + row + c);
+            for (int s = 0; s < S; ++s) x[s] = hc_load<V>(p.X + s * plane + row + c);
             if (p.y) {
-                const float yv = ld_act(p.y + row + c);
+                const HcVec<V> yv = hc_load<V>(p.y + row + c);
 #pragma unroll
                 for (int to = 0; to < S; ++to) {
-                    float a = 0.f;
 #pragma unroll
-                    for (int s = 0; s < S; ++s) a = fmaf(sh_mix[s * S + to], x[s], a);
-                    nx[to] = fmaf(sh_out[to], yv, a);
-                    p.X[to * plane + row + c] = nx[to];
+                    for (int e = 0; e < V; ++e) {
+                        float a = 0.f;
+#pragma unroll
+                        for (int s = 0; s < S; ++s) a = fmaf(sh_mix[s * S + to], x[s].v[e], a);
+                        nx[to].v[e] = fmaf(sh_out[to], yv.v[e], a);
+                    }
+                    hc_store<V>(p.X + to * plane + row + c, nx[to]);
                 }
-                if (p.zero_y) p.y[row + c] = 0.f;
+                if (p.zero_y) { HcVec<V> z; for (int e = 0; e < V; ++e) z.v[e] = 0.f; hc_store<V>(p.y + row + c, z); }
             } else {
 #pragma unroll
                 for (int s = 0; s < S; ++s) nx[s] = x[s];
             }
         }
-        float u = 0.f;
+        HcVec<V> u;
 #pragma unroll
-        for (int s = 0; s < S; ++s) u = fmaf(sh_in[s], nx[s], u);
-        u_row[c] = u;
-        if (p.u_out) p.u_out[row + c] = u;
-        ss = fmaf(u, u, ss);
+        for (int e = 0; e < V; ++e) {
+            float a = 0.f;
+#pragma unroll
+            for (int s = 0; s < S; ++s) a = fmaf(sh_in[s], nx[s].v[e], a);
+            u.v[e] = a;
+            ss = fmaf(a, a, ss);
+        }
+        hc_store<V>(u_row + c, u);
+        if (p.u_out) hc_store<V>(p.u_out + row + c, u);
     }
     if (!p.h_out) return;
     float r = 1.f;
     if (p.norm_w) r = rsqrtf(block_sum(ss, scratch) / (float)p.d + p.eps);
     TH* h = reinterpret_cast<TH*>(p.h_out) + row;
-    for (int c = threadIdx.x; c < p.d; c += HC_THREADS)          // each thread re-reads what it wrote itself
-        h[c] = from_f32<TH>(p.norm_w ? u_row[c] * r * p.norm_w[c] : u_row[c]);
+    for (int c = threadIdx.x * V; c < p.d; c += HC_THREADS * V) {      // each thread re-reads what it wrote itself
+#pragma unroll
+        for (int e = 0; e < V; ++e)
+            h[c + e] = from_f32<TH>(p.norm_w ? u_row[c + e] * r * p.norm_w[c + e] : u_row[c + e]);
+    }
 }
 
 template <typename T>
@@ -102,13 +126,20 @@ __global__ void relu2_kernel(T* z, long long n) {
     }
 }
 
-template <typename TH>
-int hc_launch(const HcParams& p, cudaStream_t stream) {
+template <typename TH, int V>
+int hc_launch_v(const HcParams& p, cudaStream_t stream) {
     const size_t smem = (size_t)p.d * sizeof(float);
-#define HC_GO(S) case S: return launch_pdl(hc_step_kernel<TH, S>, dim3(p.T), dim3(HC_THREADS), smem, stream, p)
+#define HC_GO(S) case S: return launch_pdl(hc_step_kernel<TH, S, V>, dim3(p.T), dim3(HC_THREADS), smem, stream, p)
     switch (p.S) { HC_GO(1); HC_GO(2); HC_GO(3); HC_GO(4); HC_GO(5); HC_GO(6); HC_GO(7); HC_GO(8); }
 #undef HC_GO
     return TUFF_E_SIZE;
+}
+template <typename TH>
+int hc_launch(const HcParams& p, cudaStream_t stream) {
+    // 16-byte accesses where every row starts on one: the width a multiple of 4 and the bases aligned
+    const uintptr_t bases = (uintptr_t)p.X | (uintptr_t)p.x_init | (uintptr_t)p.y | (uintptr_t)p.u_out;
+    if (p.d % 4 == 0 && (bases & 15) == 0) return hc_launch_v<TH, 4>(p, stream);
+    return hc_launch_v<TH, 1>(p, stream);
 }
 }  // namespace
 

@@ -1,0 +1,350 @@
+// Attention of single query tokens over a latent cache (bf16) on the tensor cores.
+//
+// The cache holds one row [c | kr] of hl = rank + rd elements per token, shared by all heads; the query of
+// head h is q~_h = [U_h^T q_h | rotated part] (hl elements), the score q~_h . row, and the value the first
+// `rank` elements of the same row.  All heads read the same keys, so up to 16 query heads of one token form
+// the 16-row side of mma.sync.m16n8k16 and a cached row is read once for all of them.
+//
+//   tuff_latent_decode    one CTA per (token, group of 16 heads, slice of the keys).  A tile of 64 cached
+//                         rows is brought into shared memory by cp.async (two stages; rows past the token's
+//                         position are zero-filled); warp w of eight computes the scores of keys 8w..8w+7
+//                         for all heads, the warps exchange their row maxima, write the weights (bf16) to
+//                         shared memory, and each warp accumulates its own slice of the `rank` output
+//                         columns over all 64 keys.  Scores, maxima, sums and outputs are fp32.
+//                         Every slice leaves (max, sum, weighted latents) in the workspace.
+//   tuff_latent_combine   merges the slices in slice order, lets a learned sink per head join the
+//                         denominator once, and stores the weighted latents (bf16).
+//
+// Sizes: rank and rd multiples of 8, rank <= 512, a tile pair within 227 KB of shared memory; anything else
+// is refused (TUFF_E_SIZE) and the caller uses the plain kernel.
+#include "common.cuh"
+#include "index.cuh"
+
+namespace {
+constexpr int LD_TILE = 64;        // keys per tile
+constexpr int LD_WARPS = 8;
+constexpr int LD_THREADS = LD_WARPS * 32;
+constexpr int LD_HEADS = 16;       // query heads per CTA
+constexpr int LD_PAIRS = 4;        // 16-column output blocks per warp: rank <= 8 * 4 * 16
+constexpr int LD_PLD = LD_TILE + 8;   // row length of the weights in shared memory (elements)
+constexpr int LD_MAX_SPLITS = 32;
+
+__device__ __forceinline__ uint32_t s_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+struct LatDecParams {
+    const bf16* ql;                  // [n, H, hl]
+    const bf16* k_pages;             // [pages, 1, page_size, hl]
+    const int* block_table; int max_blocks;
+    const int* positions; const int* row_of_token;
+    float* part_o;                   // [n, H, splits, rank]
+    float* part_ml;                  // [n, H, splits, 2]: maximum (in units of log2) and sum
+    int H, hl, rank, page_size, n_splits;
+    int ldq;                         // row length of queries and keys in shared memory (elements)
+    float scale_log2;
+    Bounds bounds;
+};
+
+// Rows key0 .. key0 + 63 of the request's cache into a stage; rows past `pos` become zeros.
+__device__ __forceinline__ void ld_load_tile(const LatDecParams& p, bf16* stage, const int* bt, int key0, int pos) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunks = p.hl >> 3;
+    for (int r = warp; r < LD_TILE; r += LD_WARPS) {
+        const int key = key0 + r;
+        bf16* dst = stage + (size_t)r * p.ldq;
+        const bf16* src = nullptr;
+        if (key <= pos && check_entry(p.bounds, key, p.page_size, p.max_blocks)) {
+            const long long page = ld_act(bt + page_entry(key, p.page_size));
+            if (check_page(p.bounds, page))
+                src = p.k_pages + page_elem(page, 0, page_offset(key, p.page_size), 1, p.page_size, p.hl);
+        }
+        for (int c = lane; c < chunks; c += 32) {
+            if (src) cp_async16(s_u32(dst + 8 * c), src + 8 * c);
+            else *reinterpret_cast<uint4*>(dst + 8 * c) = make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(LD_THREADS, 1)
+latent_decode_kernel(LatDecParams p) {
+    extern __shared__ __align__(16) uint8_t ld_smem[];
+    const int ldq = p.ldq;
+    bf16* Qs = reinterpret_cast<bf16*>(ld_smem);                 // [16][ldq]
+    bf16* Ks = Qs + (size_t)LD_HEADS * ldq;                       // [2][64][ldq]
+    bf16* Ps = Ks + (size_t)2 * LD_TILE * ldq;                    // [16][LD_PLD]
+    float* wmax = reinterpret_cast<float*>(Ps + LD_HEADS * LD_PLD);   // [warps][16]
+    float* wsum = wmax + LD_WARPS * LD_HEADS;                     // [warps][16]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int tok = blockIdx.x, h0 = blockIdx.y * LD_HEADS, split = blockIdx.z;
+    const int hl = p.hl, rank = p.rank;
+    const int hlp = ldq - 8;                                      // hl rounded up to a multiple of 32
+
+    // columns from hl on (of queries and of both key stages) are zero and stay so: no copy reaches them
+    for (int i = threadIdx.x; i < (LD_HEADS + 2 * LD_TILE) * (ldq - hl); i += LD_THREADS) {
+        const int r = i / (ldq - hl), c = hl + i % (ldq - hl);
+        Qs[(size_t)r * ldq + c] = __float2bfloat16_rn(0.f);
+    }
+    pdl_wait();
+    const int pos = ld_act(p.positions + tok);
+    const int row = ld_act(p.row_of_token + tok);
+    const int n_tiles = pos / LD_TILE + 1;
+    const int per = (n_tiles + p.n_splits - 1) / p.n_splits;
+    const int t_begin = split * per;
+    const int n_local = max(0, min(per, n_tiles - t_begin));
+    const bool row_fine = check_row(p.bounds, row);
+    const int* bt = p.block_table + (size_t)(row_fine ? row : 0) * p.max_blocks;
+    if (n_local == 0 || !row_fine) {                              // an empty slice: it says so
+        pdl_launch_dependents();
+        for (int i = threadIdx.x; i < LD_HEADS; i += LD_THREADS) {
+            if (h0 + i < p.H) {
+                const size_t pi = ((size_t)tok * p.H + h0 + i) * p.n_splits + split;
+                p.part_ml[pi * 2] = -INFINITY; p.part_ml[pi * 2 + 1] = 0.f;
+            }
+        }
+        return;
+    }
+    // the queries of this group's heads (zeros for heads past the last)
+    for (int i = threadIdx.x; i < LD_HEADS * (hl >> 3); i += LD_THREADS) {
+        const int r = i / (hl >> 3), c = i % (hl >> 3);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (h0 + r < p.H) v = ld_act_u4(p.ql + ((size_t)tok * p.H + h0 + r) * hl + 8 * c);
+        *reinterpret_cast<uint4*>(Qs + (size_t)r * ldq + 8 * c) = v;
+    }
+    ld_load_tile(p, Ks, bt, t_begin * LD_TILE, pos);
+
+    float o[LD_PAIRS][2][4];
+#pragma unroll
+    for (int i = 0; i < LD_PAIRS; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) o[i][j][0] = o[i][j][1] = o[i][j][2] = o[i][j][3] = 0.f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;      // rows g and g + 8
+    const int n_pairs = (rank + 15) >> 4;
+    const uint32_t q_addr = s_u32(Qs) + (uint32_t)((lane & 15) * ldq + (lane >> 4) * 8) * 2;
+    const uint32_t p_addr = s_u32(Ps) + (uint32_t)((lane & 15) * LD_PLD + (lane >> 4) * 8) * 2;
+
+    for (int i = 0; i < n_local; ++i) {
+        bf16* stage = Ks + (size_t)(i & 1) * LD_TILE * ldq;
+        cp_async_wait_all();
+        __syncthreads();                          // tile i is there, and every warp is done with tile i - 1
+        if (i + 1 < n_local)
+            ld_load_tile(p, Ks + (size_t)((i + 1) & 1) * LD_TILE * ldq, bt, (t_begin + i + 1) * LD_TILE, pos);
+        // scores of this warp's 8 keys for the 16 heads
+        float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};      // two chains of sums, added at the end
+        const uint32_t k_addr = s_u32(stage) + (uint32_t)((8 * warp + (lane & 7)) * ldq + (lane >> 3) * 8) * 2;
+        for (int kk = 0; kk < hlp; kk += 32) {
+            uint32_t a0[4], a1[4], b[4];
+            ldsm4(q_addr + kk * 2, a0);
+            ldsm4(q_addr + (kk + 16) * 2, a1);
+            ldsm4(k_addr + kk * 2, b);
+            mma_bf16(s, a0, b[0], b[1]);
+            mma_bf16(s2, a1, b[2], b[3]);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[e] += s2[e];
+        const int key = (t_begin + i) * LD_TILE + 8 * warp + 2 * t;
+        s[0] = key <= pos ? s[0] * p.scale_log2 : -INFINITY;
+        s[1] = key + 1 <= pos ? s[1] * p.scale_log2 : -INFINITY;
+        s[2] = key <= pos ? s[2] * p.scale_log2 : -INFINITY;
+        s[3] = key + 1 <= pos ? s[3] * p.scale_log2 : -INFINITY;
+        float mx_a = fmaxf(s[0], s[1]), mx_b = fmaxf(s[2], s[3]);
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        if (t == 0) { wmax[warp * LD_HEADS + g] = mx_a; wmax[warp * LD_HEADS + g + 8] = mx_b; }
+        __syncthreads();
+        float mn_a = m_a, mn_b = m_b;
+#pragma unroll
+        for (int w = 0; w < LD_WARPS; ++w) {
+            mn_a = fmaxf(mn_a, wmax[w * LD_HEADS + g]);
+            mn_b = fmaxf(mn_b, wmax[w * LD_HEADS + g + 8]);
+        }
+        const float base_a = mn_a == -INFINITY ? 0.f : mn_a, base_b = mn_b == -INFINITY ? 0.f : mn_b;
+        const float corr_a = exp2f(m_a - base_a), corr_b = exp2f(m_b - base_b);     // exp2(-inf) = 0
+        m_a = mn_a; m_b = mn_b;
+        const float p0 = exp2f(s[0] - base_a), p1 = exp2f(s[1] - base_a);
+        const float p2 = exp2f(s[2] - base_b), p3 = exp2f(s[3] - base_b);
+        l_a = l_a * corr_a + p0 + p1;
+        l_b = l_b * corr_b + p2 + p3;
+        *reinterpret_cast<uint32_t*>(Ps + g * LD_PLD + 8 * warp + 2 * t) = pack2(p0, p1);
+        *reinterpret_cast<uint32_t*>(Ps + (g + 8) * LD_PLD + 8 * warp + 2 * t) = pack2(p2, p3);
+        __syncthreads();
+        // this warp's output columns over the tile's 64 keys
+#pragma unroll
+        for (int u = 0; u < LD_PAIRS; ++u)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) { o[u][j][0] *= corr_a; o[u][j][1] *= corr_a; o[u][j][2] *= corr_b; o[u][j][3] *= corr_b; }
+#pragma unroll
+        for (int j = 0; j < LD_TILE / 16; ++j) {
+            uint32_t pa[4];
+            ldsm4(p_addr + j * 32, pa);
+            const int m = lane >> 3;
+            const uint32_t v_addr = s_u32(stage) + (uint32_t)((16 * j + 8 * (m & 1) + (lane & 7)) * ldq + (m >> 1) * 8) * 2;
+#pragma unroll
+            for (int u = 0; u < LD_PAIRS; ++u) {
+                const int pr = warp + LD_WARPS * u;
+                if (pr < n_pairs) {
+                    uint32_t r[4];
+                    ldsm4_trans(v_addr + pr * 32, r);
+                    mma_bf16(o[u][0], pa, r[0], r[1]);
+                    mma_bf16(o[u][1], pa, r[2], r[3]);
+                }
+            }
+        }
+    }
+    pdl_launch_dependents();
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    if (t == 0) { wsum[warp * LD_HEADS + g] = l_a; wsum[warp * LD_HEADS + g + 8] = l_b; }
+    __syncthreads();
+    if (warp == 0 && t == 0) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = g + 8 * half;
+            if (h0 + r < p.H) {
+                float L = 0.f;
+#pragma unroll
+                for (int w = 0; w < LD_WARPS; ++w) L += wsum[w * LD_HEADS + r];
+                const size_t pi = ((size_t)tok * p.H + h0 + r) * p.n_splits + split;
+                p.part_ml[pi * 2] = half ? m_b : m_a;
+                p.part_ml[pi * 2 + 1] = L;
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < LD_PAIRS; ++u) {
+        const int pr = warp + LD_WARPS * u;
+        if (pr >= n_pairs) continue;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int col = 16 * pr + 8 * j + 2 * t;
+            if (col >= rank) continue;                           // rank is a multiple of 8: col + 1 < rank as well
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = g + 8 * half;
+                if (h0 + r >= p.H) continue;
+                const size_t pi = ((size_t)tok * p.H + h0 + r) * p.n_splits + split;
+                *reinterpret_cast<float2*>(p.part_o + pi * rank + col) = make_float2(o[u][j][2 * half], o[u][j][2 * half + 1]);
+            }
+        }
+    }
+}
+
+// A block per (token, head, 128 columns): the slices' partial results in slice order, then the sink.  The first warp
+// turns the slices' maxima and sums into one weight per slice (a lane per slice), the block then adds the
+// slices' weighted latents column by column.
+__global__ void __launch_bounds__(128)
+latent_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
+                      int n_splits, const float* __restrict__ sinks, int H, int rank) {
+    __shared__ float wgt[LD_MAX_SPLITS];
+    const size_t th = blockIdx.x;
+    const bool has_sink = sinks != nullptr;
+    const float sink_log2 = has_sink ? sinks[th % H] * 1.4426950408889634f : 0.f;
+    pdl_wait();
+    pdl_launch_dependents();
+    if (threadIdx.x < 32) {
+        const int s = threadIdx.x;
+        const float* ml = part_ml + th * n_splits * 2;
+        const float ms = s < n_splits ? ld_act(ml + 2 * s) : -INFINITY;
+        const float ls = s < n_splits ? ld_act(ml + 2 * s + 1) : 0.f;
+        float M = fmaxf(ms, has_sink ? sink_log2 : -INFINITY);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float e = ms == -INFINITY ? 0.f : exp2f(ms - M);
+        float L = ls * e;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);      // the same tree whatever the slices hold
+        if (has_sink) L += exp2f(sink_log2 - M);
+        if (s < LD_MAX_SPLITS) wgt[s] = L > 0.f ? e / L : 0.f;
+    }
+    __syncthreads();
+    const float* po = part_o + th * n_splits * rank;
+    for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < rank; d += gridDim.y * blockDim.x) {
+        float O = 0.f;
+#pragma unroll 4
+        for (int s = 0; s < n_splits; ++s) {
+            const float w = wgt[s];
+            if (w != 0.f) O = fmaf(ld_act(po + (size_t)s * rank + d), w, O);         // an empty slice wrote nothing
+        }
+        out[th * rank + d] = __float2bfloat16_rn(O);
+    }
+}
+
+int ld_row_len(int hl) { return ((hl + 31) / 32) * 32 + 8; }
+size_t ld_smem_bytes(int hl) {
+    return (size_t)(LD_HEADS + 2 * LD_TILE) * ld_row_len(hl) * 2 + (size_t)LD_HEADS * LD_PLD * 2 + 2 * LD_WARPS * LD_HEADS * 4;
+}
+}  // namespace
+
+extern "C" int tuff_latent_decode_supported(int H, int rank, int rd) {
+    if (H < 1 || rank < 8 || (rank % 8) || rd < 0 || (rd % 8) || rank > LD_WARPS * LD_PAIRS * 16) return 0;
+    return ld_smem_bytes(rank + rd) <= 227 * 1024 ? 1 : 0;
+}
+
+// How many slices of the keys for `n_tokens` query tokens at contexts up to `max_seq_len`.
+extern "C" int tuff_latent_decode_splits(int n_tokens, int H, int max_seq_len) {
+    const int tiles = (max_seq_len + LD_TILE - 1) / LD_TILE;
+    const int ctas = n_tokens * ceil_div(H, LD_HEADS);
+    int want = sm_count() / ctas;                           // one CTA per SM at a time: one round
+    if (const char* e = getenv("TUFF_LATENT_SPLITS")) { const int v = atoi(e); if (v > 0) want = v; }
+    if (want > tiles) want = tiles;
+    if (want > LD_MAX_SPLITS) want = LD_MAX_SPLITS;
+    return want < 1 ? 1 : want;
+}
+extern "C" long long tuff_latent_decode_workspace_floats(int n_tokens, int H, int rank, int n_splits) {
+    return (long long)n_tokens * H * n_splits * (rank + 2);
+}
+
+// ql [n, H, rank + rd], k_pages [pages, 1, page_size, rank + rd] (bf16), out [n, H, rank] (bf16): the weighted
+// latents of every head; sinks [H] fp32 or null; ws: the workspace (see above), 16-byte aligned.
+extern "C" int tuff_latent_decode(const void* ql, const void* k_pages, const int* block_table, int max_blocks,
+                                  const int* positions, const int* row_of_token, void* out, float* ws, int n_splits,
+                                  int n_tokens, int H, int rank, int rd, int page_size, float scale, const float* sinks,
+                                  long long table_rows, long long n_pages, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (!tuff_latent_decode_supported(H, rank, rd) || page_size < 1 || n_splits < 1 || n_splits > LD_MAX_SPLITS) return TUFF_E_SIZE;
+    if (((uintptr_t)ql & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)ws & 15)) return TUFF_E_ALIGN;
+    const int hl = rank + rd;
+    const size_t smem = ld_smem_bytes(hl);
+    static bool raised = false;
+    if (!raised) {
+        const cudaError_t e = cudaFuncSetAttribute(latent_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    LatDecParams p;
+    p.ql = (const bf16*)ql; p.k_pages = (const bf16*)k_pages; p.block_table = block_table; p.max_blocks = max_blocks;
+    p.positions = positions; p.row_of_token = row_of_token;
+    p.part_o = ws;
+    p.part_ml = ws + (size_t)n_tokens * H * n_splits * rank;
+    p.H = H; p.hl = hl; p.rank = rank; p.page_size = page_size; p.n_splits = n_splits; p.ldq = ld_row_len(hl);
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.bounds = Bounds{table_rows, n_pages, status};
+    int rc = launch_pdl(latent_decode_kernel, dim3(n_tokens, ceil_div(H, LD_HEADS), n_splits), dim3(LD_THREADS), smem, stream, p);
+    if (rc) return rc;
+    return launch_pdl(latent_combine_kernel, dim3(n_tokens * H, ceil_div(rank, 128)), dim3(128), 0, stream, (const float*)p.part_o,
+                      (const float*)p.part_ml, (bf16*)out, n_splits, sinks, H, rank);
+}

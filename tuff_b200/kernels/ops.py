@@ -208,6 +208,9 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: 
                                c_longlong(out.stride(0)), c_int(1 if accumulate else 0), _stream()), "gemm_plain")
 
 
+HEAD_ROWS_MAX = 128      # token counts up to this take the few-rows kernel of head_linear
+
+
 def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """A projection with a matrix of its own per head: out[t, h, :] = w[h] @ a[t, h, :], for a [T, H, K] and
     out [T, H, N] (views whose last dimension is contiguous and whose head stride is any number of
@@ -218,6 +221,13 @@ def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     assert w.shape == (H, N, K) and out.shape == (T, H, N) and a.stride(2) == 1 and out.stride(2) == 1
     _contig(w, "w")
     lib = load_library("gemm_plain")
+    if (a.dtype == w.dtype == out.dtype == torch.bfloat16 and T <= HEAD_ROWS_MAX and K % 2 == 0
+            and not (a.stride(0) | a.stride(1)) & 1 and not (a.data_ptr() | w.data_ptr()) & 3):
+        # few tokens: one warp per output column, the matrices read once per eight tokens
+        _check(lib.tuff_head_rows(_ptr(a), _ptr(w), _ptr(out), c_int(T), c_int(N), c_int(K), c_longlong(a.stride(0)),
+                                  c_longlong(K), c_longlong(out.stride(0)), c_int(H), c_longlong(a.stride(1)),
+                                  c_longlong(N * K), c_longlong(out.stride(1)), _stream()), "head_linear")
+        return
     _check(lib.tuff_gemm_plain_batched(_ptr(a), dtype_code(a), _ptr(w), dtype_code(w), _ptr(out), dtype_code(out),
                                        c_int(T), c_int(N), c_int(K), c_longlong(a.stride(0)), c_longlong(K),
                                        c_longlong(out.stride(0)), c_int(H), c_longlong(a.stride(1)), c_longlong(N * K),
@@ -790,6 +800,56 @@ def latent_expand_store(kv: torch.Tensor, k_pages: torch.Tensor, block_table: to
                                         c_int(rank), c_int(k_pages.shape[2]), c_longlong(block_table.shape[0]),
                                         c_longlong(k_pages.shape[0]), _ptr(status_word(k_pages.device)), _stream()),
            "latent_expand_store")
+
+
+def latent_decode_supported(ql: torch.Tensor, k_pages: torch.Tensor, H: int, rank: int, rd: int) -> bool:
+    """Whether the tensor-core kernel for single tokens over a latent cache takes these sizes (bf16)."""
+    if ql.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16 or os.environ.get("TUFF_LATENT_DECODE", "1") == "0":
+        return False
+    return bool(load_library("latent_decode").tuff_latent_decode_supported(c_int(H), c_int(rank), c_int(rd)))
+
+
+def reserve_latent_workspace(device, max_rows: int, max_context: int, heads: int, rank: int, rd: int) -> None:
+    """Sizes the workspace of `latent_decode` once for up to `max_rows` tokens at contexts up to `max_context`."""
+    device = torch.device(device)
+    with torch.cuda.device(device):
+        lib = load_library("latent_decode")
+        if not lib.tuff_latent_decode_supported(c_int(heads), c_int(rank), c_int(rd)):
+            return
+        lib.tuff_latent_decode_workspace_floats.restype = c_longlong
+        need = 0
+        for n in range(1, max(1, max_rows) + 1):
+            splits = lib.tuff_latent_decode_splits(c_int(n), c_int(heads), c_int(max(1, max_context)))
+            need = max(need, lib.tuff_latent_decode_workspace_floats(c_int(n), c_int(heads), c_int(rank), c_int(splits)))
+        _attn_workspace(device, int(need))
+
+
+def latent_decode(ql: torch.Tensor, k_pages: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,
+                  row_of_token: torch.Tensor, out: torch.Tensor, H: int, rank: int, rd: int, scale: float,
+                  sink: torch.Tensor | None = None, max_seq_len: int | None = None) -> None:
+    """Attention of single tokens over a latent cache (bf16) on the tensor cores.  ql [n, H, rank + rd] are
+    the queries in the latent space, k_pages [pages, 1, page, rank + rd] the cached rows [c | kr], out
+    [n, H, rank] the weighted latents of every head (token t sees the rows 0..positions[t] of its request);
+    `sink` [H] fp32 joins the softmax's denominator.  The keys of a token are cut into slices that run in
+    parallel; `max_seq_len` (an upper bound on the contexts) sizes the cut."""
+    _written(out)
+    n = ql.shape[0]
+    hl = rank + rd
+    assert ql.shape == (n, H, hl) and out.shape == (n, H, rank) and k_pages.shape[1] == 1 and k_pages.shape[3] == hl
+    _contig(ql, "ql"); _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(block_table, "block_table")
+    _i32(block_table, "block_table"); _i32(positions, "positions"); _i32(row_of_token, "row_of_token")
+    if sink is not None:
+        assert sink.dtype == torch.float32 and sink.numel() == H
+    lib = load_library("latent_decode")
+    bound = int(max_seq_len) if max_seq_len else block_table.shape[1] * k_pages.shape[2]
+    splits = lib.tuff_latent_decode_splits(c_int(n), c_int(H), c_int(max(1, bound)))
+    lib.tuff_latent_decode_workspace_floats.restype = c_longlong
+    ws = _attn_workspace(ql.device, lib.tuff_latent_decode_workspace_floats(c_int(n), c_int(H), c_int(rank), c_int(splits)))
+    _check(lib.tuff_latent_decode(_ptr(ql), _ptr(k_pages), _ptr(block_table), c_int(block_table.shape[1]), _ptr(positions),
+                                  _ptr(row_of_token), _ptr(out), _ptr(ws), c_int(splits), c_int(n), c_int(H), c_int(rank),
+                                  c_int(rd), c_int(k_pages.shape[2]), c_float(scale), _ptr(sink),
+                                  c_longlong(block_table.shape[0]), c_longlong(k_pages.shape[0]),
+                                  _ptr(status_word(ql.device)), _stream()), "latent_decode", kernels=2)
 
 
 def paged_attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,

@@ -9,7 +9,9 @@ Only [c | kr] is cached, one row per token in pages of a single key/value head. 
 into the latent space instead of the cache being expanded: q~_h = [U_h^T q_plain | q_rot], so that the score
 is q~_h . [c | kr]; attention runs over the cached rows with the values being the rows' first `kv_rank`
 elements, and V_h is applied to the weighted sum of latents afterwards.  This is the same sum in another
-order; scores, softmax, the norm of c and the rotation are fp32.
+order; scores, softmax, the norm of c and the rotation are fp32.  In bf16 all heads of a token share one pass
+over its cached rows (`ops.latent_decode`: up to 16 heads are the rows of a tensor-core tile, the keys cut into
+slices that run in parallel); other types and sizes take the plain paged kernel.
 
 Portions of prompts (bf16, heads of 64 or 128 with values as wide) take the other order: a portion has as many
 queries as keys, so the cached rows of its request are expanded once into keys [U_h c | kr] and values V_h c per
@@ -80,6 +82,9 @@ class LatentAttention(Mixer):
         hq = self.dim + self.rd
         self.expands = (act_dtype == torch.bfloat16 and hq == self.vd and hq in (64, 128)
                         and self.dim % 8 == 0 and self.rd % 8 == 0 and self.rank % 8 == 0)
+        # single tokens in the latent form: the tensor-core kernel where it takes the sizes, else the plain one
+        self.decodes_tc = (act_dtype == torch.bfloat16 and self.wo.is_cuda
+                           and ops.latent_decode_supported(self.wo, self.wo, H, self.rank, self.rd))
         self.w_exp = torch.cat([weights["uk"], weights["uv"]], dim=0).contiguous() if self.expands else None
 
     # ---- scratch pages of expanded keys and values: one buffer per device, shared by all layers ---------------------
@@ -104,6 +109,8 @@ class LatentAttention(Mixer):
         return out
 
     def reserve(self, device, max_rows, max_context):
+        if self.decodes_tc:
+            ops.reserve_latent_workspace(device, max_rows, max_context, self.H, self.rank, self.rd)
         if self.expands:
             device = torch.device(device)
             self._cap_pages = -(-max(int(max_context), 8192) // ops.latent_scratch_page()) + 4
@@ -167,11 +174,15 @@ class LatentAttention(Mixer):
                                H, dim, rd, rank, self.rot_dims, self.eps, write_kv=not reads_only)
             ops.head_linear(qd[:n1, : H * hq].unflatten(1, (H, hq))[:, :, :dim], self.ukt, ql[:n1, :, :rank])
             lat = torch.empty((n1, H * rank), dtype=self.act_dtype, device=dev)
-            ops.paged_attention(ql[:n1].view(n1, H * hl), cache.k_pages, None, table[:ctx.single_prefix] if expand else table,
-                                ctx.positions[:n1], ctx.row_of_token[:n1], lat, H, 1, hl, self.scale, 0,
-                                cu_q=None if expand else ctx.cu_q, all_single=True if expand else ctx.all_single,
-                                max_seq_len=ctx.max_seq_len, single_prefix=0 if expand else ctx.single_prefix,
-                                sink=self.sinks, v_head_dim=rank, values_in_keys=True)
+            if self.decodes_tc:
+                ops.latent_decode(ql[:n1], cache.k_pages, table, ctx.positions[:n1], ctx.row_of_token[:n1], lat.view(n1, H, rank),
+                                  H, rank, rd, self.scale, sink=self.sinks, max_seq_len=ctx.max_seq_len)
+            else:
+                ops.paged_attention(ql[:n1].view(n1, H * hl), cache.k_pages, None, table[:ctx.single_prefix] if expand else table,
+                                    ctx.positions[:n1], ctx.row_of_token[:n1], lat, H, 1, hl, self.scale, 0,
+                                    cu_q=None if expand else ctx.cu_q, all_single=True if expand else ctx.all_single,
+                                    max_seq_len=ctx.max_seq_len, single_prefix=0 if expand else ctx.single_prefix,
+                                    sink=self.sinks, v_head_dim=rank, values_in_keys=True)
             ops.head_linear(lat.view(n1, H, rank), self.uv, att[:n1])
         if n1 < T:
             # the portions: rotated queries in place (the cache rows are written by the first call, if there was one)
