@@ -65,21 +65,28 @@ struct LatDecParams {
     Bounds bounds;
 };
 
-// Rows key0 .. key0 + 63 of the request's cache into a stage; rows past `pos` become zeros.
+// Rows key0 .. key0 + 63 of the request's cache into a stage; rows past `pos` become zeros.  Warp w takes rows
+// w, w + 8, ...; its lanes look the rows' pages up side by side (lane i the i-th of them) before any copy is issued,
+// so the table's latency is paid once a tile and not once a row.
 __device__ __forceinline__ void ld_load_tile(const LatDecParams& p, bf16* stage, const int* bt, int key0, int pos) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int chunks = p.hl >> 3;
-    for (int r = warp; r < LD_TILE; r += LD_WARPS) {
-        const int key = key0 + r;
-        bf16* dst = stage + (size_t)r * p.ldq;
-        const bf16* src = nullptr;
+    constexpr int PER_WARP = LD_TILE / LD_WARPS;
+    long long my_off = -1;                                        // element offset of this lane's row in the pool
+    {
+        const int key = key0 + warp + LD_WARPS * (lane % PER_WARP);
         if (key <= pos && check_entry(p.bounds, key, p.page_size, p.max_blocks)) {
             const long long page = ld_act(bt + page_entry(key, p.page_size));
-            if (check_page(p.bounds, page))
-                src = p.k_pages + page_elem(page, 0, page_offset(key, p.page_size), 1, p.page_size, p.hl);
+            if (check_page(p.bounds, page)) my_off = (long long)page_elem(page, 0, page_offset(key, p.page_size), 1, p.page_size, p.hl);
         }
+    }
+#pragma unroll
+    for (int i = 0; i < PER_WARP; ++i) {
+        const long long off = __shfl_sync(0xffffffffu, my_off, i);
+        bf16* dst = stage + (size_t)(warp + LD_WARPS * i) * p.ldq;
+        const bf16* src = p.k_pages + off;
         for (int c = lane; c < chunks; c += 32) {
-            if (src) cp_async16(s_u32(dst + 8 * c), src + 8 * c);
+            if (off >= 0) cp_async16(s_u32(dst + 8 * c), src + 8 * c);
             else *reinterpret_cast<uint4*>(dst + 8 * c) = make_uint4(0u, 0u, 0u, 0u);
         }
     }
@@ -124,14 +131,14 @@ latent_decode_kernel(LatDecParams p) {
         }
         return;
     }
-    // the queries of this group's heads (zeros for heads past the last)
+    ld_load_tile(p, Ks, bt, t_begin * LD_TILE, pos);
+    // the queries of this group's heads (zeros for heads past the last), while the first tile is on its way
     for (int i = threadIdx.x; i < LD_HEADS * (hl >> 3); i += LD_THREADS) {
         const int r = i / (hl >> 3), c = i % (hl >> 3);
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (h0 + r < p.H) v = ld_act_u4(p.ql + ((size_t)tok * p.H + h0 + r) * hl + 8 * c);
         *reinterpret_cast<uint4*>(Qs + (size_t)r * ldq + 8 * c) = v;
     }
-    ld_load_tile(p, Ks, bt, t_begin * LD_TILE, pos);
 
     float o[LD_PAIRS][2][4];
 #pragma unroll
