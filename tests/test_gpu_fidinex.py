@@ -473,7 +473,8 @@ def test_latent_decode_kernel_far_keys_and_sinks(monkeypatch, H, rank, rd, page,
                 assert np.abs(got[i, hot[-1]] - rows[0, key_at, :rank]).max() < 0.1
 
 
-@pytest.mark.parametrize("T,H,K,N", [(1, 3, 16, 20), (8, 16, 64, 128), (9, 5, 130, 7), (64, 2, 512, 64), (128, 1, 24, 33)])
+@pytest.mark.parametrize("T,H,K,N", [(1, 3, 16, 20), (8, 16, 64, 128), (9, 5, 130, 7), (64, 2, 512, 64), (128, 1, 24, 33), (17, 2, 1024, 70),
+                                     (3, 4, 5, 64)])
 def test_head_linear_of_few_rows(T, H, K, N):
     """A matrix per head applied to views with strides (heads inside wider rows), few tokens: the one-warp-per-column kernel."""
     from tuff_b200.kernels import ops
@@ -482,10 +483,12 @@ def test_head_linear_of_few_rows(T, H, K, N):
     wide = dev(rng.normal(size=(T, H, K + 6)), bf)
     w = dev(rng.normal(size=(H, N, K)) / math.sqrt(K), bf)
     outw = torch.zeros(T, H, N + 2, device="cuda", dtype=bf)
-    ops.head_linear(wide[:, :, 2:2 + K], w, outw[:, :, :N])
     ref = np.einsum("thk,hnk->thn", f64(wide[:, :, 2:2 + K]), f64(w))
-    assert np.abs(f64(outw[:, :, :N]) - ref).max() <= 1e-2 * max(1.0, np.abs(ref).max())
-    assert float(outw[:, :, N:].abs().max()) == 0.0
+    for wt in (None, w.transpose(1, 2).contiguous()):        # a warp per column; a thread per column of the transposed matrices
+        outw.zero_()
+        ops.head_linear(wide[:, :, 2:2 + K], w, outw[:, :, :N], wt=wt)
+        assert np.abs(f64(outw[:, :, :N]) - ref).max() <= 1e-2 * max(1.0, np.abs(ref).max())
+        assert float(outw[:, :, N:].abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("hd,vd,page", [(16, 16, 4), (64, 64, 16), (128, 128, 32), (24, 40, 8)])

@@ -112,6 +112,52 @@ head_rows_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, bf16* _
     }
     if (lane < rows) C[(size_t)lane * ldc + n] = __float2bfloat16_rn(mine);
 }
+// The same batch with the matrices stored [batch][K][N] (N contiguous), bf16: C[m, n] = sum_k A[m, k] Wt[k, n].
+// A thread owns one column n for HC_ROWS rows and a quarter of K (threadIdx.y); neighbouring threads read
+// neighbouring columns of a row of Wt, the rows of A come from shared memory as broadcasts.  The four partial
+// sums are added in the order of the quarters, so an element's value depends on K alone.
+constexpr int HC_COLS = 64, HC_KPARTS = 4, HC_ROWS = 8, HC_MAX_K = 1024;
+__global__ void __launch_bounds__(HC_COLS * HC_KPARTS)
+head_cols_kernel(const bf16* __restrict__ A, const bf16* __restrict__ Wt, bf16* __restrict__ C, int M, int N, int K,
+                 long long lda, long long ldc, long long sa, long long sw, long long sc) {
+    __shared__ float a_s[HC_ROWS][HC_MAX_K];
+    __shared__ float part[HC_KPARTS][HC_ROWS][HC_COLS];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const int n = blockIdx.x * HC_COLS + tx, m0 = blockIdx.z * HC_ROWS;
+    const int rows = min(HC_ROWS, M - m0);
+    A += (size_t)blockIdx.y * sa + (size_t)m0 * lda; Wt += (size_t)blockIdx.y * sw; C += (size_t)blockIdx.y * sc + (size_t)m0 * ldc;
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int i = ty * HC_COLS + tx; i < HC_ROWS * K; i += HC_COLS * HC_KPARTS) {
+        const int r = i / K, k = i % K;
+        a_s[r][k] = r < rows ? ld_act(A + (size_t)r * lda + k) : 0.f;
+    }
+    __syncthreads();
+    const int per = (K + HC_KPARTS - 1) / HC_KPARTS;
+    const int k0 = ty * per, k1 = min(K, k0 + per);
+    float acc[HC_ROWS];
+#pragma unroll
+    for (int i = 0; i < HC_ROWS; ++i) acc[i] = 0.f;
+    if (n < N) {
+#pragma unroll 4
+        for (int k = k0; k < k1; ++k) {
+            const float w = __bfloat162float(Wt[(size_t)k * N + n]);
+#pragma unroll
+            for (int i = 0; i < HC_ROWS; ++i) acc[i] = fmaf(a_s[i][k], w, acc[i]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < HC_ROWS; ++i) part[ty][i][tx] = acc[i];
+    __syncthreads();
+    if (n < N) {
+        for (int i = ty; i < rows; i += HC_KPARTS) {
+            float v = part[0][i][tx];
+#pragma unroll
+            for (int q = 1; q < HC_KPARTS; ++q) v += part[q][i][tx];
+            C[(size_t)i * ldc + n] = __float2bfloat16_rn(v);
+        }
+    }
+}
 }  // namespace
 
 // `batch` products in one launch: product b reads A + b*sa, W + b*sw and writes C + b*sc (strides in elements).
@@ -158,4 +204,14 @@ extern "C" int tuff_head_rows(const void* A, const void* W, void* C, int M, int 
     if (((uintptr_t)A | (uintptr_t)W) & 3) return TUFF_E_ALIGN;
     return launch_pdl(head_rows_kernel, dim3(ceil_div(N, HR_WARPS), batch, ceil_div(M, HR_ROWS)), dim3(HR_WARPS * 32), 0, stream,
                       (const bf16*)A, (const bf16*)W, (bf16*)C, M, N, K, lda, ldw, ldc, sa, sw, sc);
+}
+
+// The same batch with the matrices given transposed, Wt [batch][K][N] contiguous (product b reads Wt + b*sw), bf16
+// throughout, K up to 1,024: a thread per output column.  Larger K: TUFF_E_SIZE, and the caller takes another kernel.
+extern "C" int tuff_head_cols(const void* A, const void* Wt, void* C, int M, int N, int K, long long lda, long long ldc,
+                              int batch, long long sa, long long sw, long long sc, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    if (K <= 0 || K > HC_MAX_K || batch > 65535 || ceil_div(M, HC_ROWS) > 65535) return TUFF_E_SIZE;
+    return launch_pdl(head_cols_kernel, dim3(ceil_div(N, HC_COLS), batch, ceil_div(M, HC_ROWS)), dim3(HC_COLS, HC_KPARTS), 0, stream,
+                      (const bf16*)A, (const bf16*)Wt, (bf16*)C, M, N, K, lda, ldc, sa, sw, sc);
 }

@@ -66,22 +66,24 @@ struct LatDecParams {
 };
 
 // Rows key0 .. key0 + 63 of the request's cache into a stage; rows past `pos` become zeros.  Warp w takes rows
-// w, w + 8, ...; its lanes look the rows' pages up side by side (lane i the i-th of them) before any copy is issued,
-// so the table's latency is paid once a tile and not once a row.
-__device__ __forceinline__ void ld_load_tile(const LatDecParams& p, bf16* stage, const int* bt, int key0, int pos) {
+// w, w + 8, ...; its lanes look the rows' pages up side by side (lane i the i-th of them), and a tile's lookup is
+// made one tile ahead of its copies, so the table's latency hides behind the tile before.
+constexpr int LD_PER_WARP = LD_TILE / LD_WARPS;
+__device__ __forceinline__ long long ld_lookup(const LatDecParams& p, const int* bt, int key0, int pos) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int key = key0 + warp + LD_WARPS * (lane % LD_PER_WARP);
+    long long off = -1;                                           // element offset of this lane's row in the pool
+    if (key <= pos && check_entry(p.bounds, key, p.page_size, p.max_blocks)) {
+        const long long page = ld_act(bt + page_entry(key, p.page_size));
+        if (check_page(p.bounds, page)) off = (long long)page_elem(page, 0, page_offset(key, p.page_size), 1, p.page_size, p.hl);
+    }
+    return off;
+}
+__device__ __forceinline__ void ld_copy_tile(const LatDecParams& p, bf16* stage, long long my_off) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int chunks = p.hl >> 3;
-    constexpr int PER_WARP = LD_TILE / LD_WARPS;
-    long long my_off = -1;                                        // element offset of this lane's row in the pool
-    {
-        const int key = key0 + warp + LD_WARPS * (lane % PER_WARP);
-        if (key <= pos && check_entry(p.bounds, key, p.page_size, p.max_blocks)) {
-            const long long page = ld_act(bt + page_entry(key, p.page_size));
-            if (check_page(p.bounds, page)) my_off = (long long)page_elem(page, 0, page_offset(key, p.page_size), 1, p.page_size, p.hl);
-        }
-    }
 #pragma unroll
-    for (int i = 0; i < PER_WARP; ++i) {
+    for (int i = 0; i < LD_PER_WARP; ++i) {
         const long long off = __shfl_sync(0xffffffffu, my_off, i);
         bf16* dst = stage + (size_t)(warp + LD_WARPS * i) * p.ldq;
         const bf16* src = p.k_pages + off;
@@ -131,7 +133,8 @@ latent_decode_kernel(LatDecParams p) {
         }
         return;
     }
-    ld_load_tile(p, Ks, bt, t_begin * LD_TILE, pos);
+    ld_copy_tile(p, Ks, ld_lookup(p, bt, t_begin * LD_TILE, pos));
+    long long off_next = n_local > 1 ? ld_lookup(p, bt, (t_begin + 1) * LD_TILE, pos) : -1;
     // the queries of this group's heads (zeros for heads past the last), while the first tile is on its way
     for (int i = threadIdx.x; i < LD_HEADS * (hl >> 3); i += LD_THREADS) {
         const int r = i / (hl >> 3), c = i % (hl >> 3);
@@ -154,8 +157,8 @@ latent_decode_kernel(LatDecParams p) {
         bf16* stage = Ks + (size_t)(i & 1) * LD_TILE * ldq;
         cp_async_wait_all();
         __syncthreads();                          // tile i is there, and every warp is done with tile i - 1
-        if (i + 1 < n_local)
-            ld_load_tile(p, Ks + (size_t)((i + 1) & 1) * LD_TILE * ldq, bt, (t_begin + i + 1) * LD_TILE, pos);
+        if (i + 1 < n_local) ld_copy_tile(p, Ks + (size_t)((i + 1) & 1) * LD_TILE * ldq, off_next);
+        if (i + 2 < n_local) off_next = ld_lookup(p, bt, (t_begin + i + 2) * LD_TILE, pos);      // used one tile later
         // scores of this warp's 8 keys for the 16 heads
         float s[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};      // two chains of sums, added at the end
         const uint32_t k_addr = s_u32(stage) + (uint32_t)((8 * warp + (lane & 7)) * ldq + (lane >> 3) * 8) * 2;

@@ -208,19 +208,32 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: 
                                c_longlong(out.stride(0)), c_int(1 if accumulate else 0), _stream()), "gemm_plain")
 
 
-HEAD_ROWS_MAX = 128      # token counts up to this take the few-rows kernel of head_linear
+HEAD_ROWS_MAX = 128      # token counts up to this take the few-rows kernels of head_linear
+HEAD_COLS_MAX_K = 1024   # the widest input of its column-per-thread kernel
+HEAD_COLS_MIN = 16       # more tokens than this take it when the transposed matrices are given (measured: at 8 tokens the
+                         # warp-per-column kernel needs 9 us where this one needs 15, at 64 tokens 29 against 16)
 
 
-def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+def head_linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, wt: torch.Tensor | None = None) -> None:
     """A projection with a matrix of its own per head: out[t, h, :] = w[h] @ a[t, h, :], for a [T, H, K] and
     out [T, H, N] (views whose last dimension is contiguous and whose head stride is any number of
-    elements) and w [H, N, K] contiguous.  FFMA with fp32 sums in ascending k, all heads in one launch."""
+    elements) and w [H, N, K] contiguous.  FFMA with fp32 sums in ascending k, all heads in one launch.
+    `wt` [H, K, N]: the same matrices transposed, for the kernel that 17 to 128 bf16 tokens take when it is given
+    (a thread per output column, neighbouring threads on neighbouring columns); fewer tokens take a warp per column."""
     _written(out)
     T, H, K = a.shape
     N = w.shape[1]
     assert w.shape == (H, N, K) and out.shape == (T, H, N) and a.stride(2) == 1 and out.stride(2) == 1
     _contig(w, "w")
     lib = load_library("gemm_plain")
+    if (wt is not None and a.dtype == wt.dtype == out.dtype == torch.bfloat16 and HEAD_COLS_MIN < T <= HEAD_ROWS_MAX
+            and K <= HEAD_COLS_MAX_K):
+        assert wt.shape == (H, K, N)
+        _contig(wt, "wt")
+        _check(lib.tuff_head_cols(_ptr(a), _ptr(wt), _ptr(out), c_int(T), c_int(N), c_int(K), c_longlong(a.stride(0)),
+                                  c_longlong(out.stride(0)), c_int(H), c_longlong(a.stride(1)), c_longlong(N * K),
+                                  c_longlong(out.stride(1)), _stream()), "head_linear")
+        return
     if (a.dtype == w.dtype == out.dtype == torch.bfloat16 and T <= HEAD_ROWS_MAX and K % 2 == 0
             and not (a.stride(0) | a.stride(1)) & 1 and not (a.data_ptr() | w.data_ptr()) & 3):
         # few tokens: one warp per output column, the matrices read once per eight tokens

@@ -71,6 +71,10 @@ class LatentAttention(Mixer):
         # U_h^T as the matrix of a product: [H, kv_rank, dim]; V_h: [H, vdim, kv_rank]
         self.ukt = weights["uk"].view(H, self.dim, self.rank).transpose(1, 2).contiguous()
         self.uv = weights["uv"].view(H, self.vd, self.rank).contiguous()
+        # the same matrices the other way round, [H, in, out], for the products of few bf16 tokens
+        bf = act_dtype == torch.bfloat16
+        self.ukt_t = weights["uk"].view(H, self.dim, self.rank) if bf else None
+        self.uv_t = self.uv.transpose(1, 2).contiguous() if bf else None
         self.wo = weights["o"]
         self.c_norm = weights["dkv_norm"]
         self.sinks = weights["sink"].contiguous() if self.learned_sink else None
@@ -172,7 +176,7 @@ class LatentAttention(Mixer):
             ql = torch.empty((T, H, hl), dtype=self.act_dtype, device=dev)          # the query in the latent space
             ops.latent_prepare(qd, ql, self.c_norm, self._inv_freq, ctx.positions, ctx.row_of_token, table, cache.k_pages,
                                H, dim, rd, rank, self.rot_dims, self.eps, write_kv=not reads_only)
-            ops.head_linear(qd[:n1, : H * hq].unflatten(1, (H, hq))[:, :, :dim], self.ukt, ql[:n1, :, :rank])
+            ops.head_linear(qd[:n1, : H * hq].unflatten(1, (H, hq))[:, :, :dim], self.ukt, ql[:n1, :, :rank], wt=self.ukt_t)
             lat = torch.empty((n1, H * rank), dtype=self.act_dtype, device=dev)
             if self.decodes_tc:
                 ops.latent_decode(ql[:n1], cache.k_pages, table, ctx.positions[:n1], ctx.row_of_token[:n1], lat.view(n1, H, rank),
@@ -183,7 +187,7 @@ class LatentAttention(Mixer):
                                     cu_q=None if expand else ctx.cu_q, all_single=True if expand else ctx.all_single,
                                     max_seq_len=ctx.max_seq_len, single_prefix=0 if expand else ctx.single_prefix,
                                     sink=self.sinks, v_head_dim=rank, values_in_keys=True)
-            ops.head_linear(lat.view(n1, H, rank), self.uv, att[:n1])
+            ops.head_linear(lat.view(n1, H, rank), self.uv, att[:n1], wt=self.uv_t)
         if n1 < T:
             # the portions: rotated queries in place (the cache rows are written by the first call, if there was one)
             ops.latent_prepare(qd, None, self.c_norm, self._inv_freq, ctx.positions, ctx.row_of_token, table, cache.k_pages,
